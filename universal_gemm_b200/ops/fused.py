@@ -1,0 +1,348 @@
+"""Host side of the fused stationary GEMM: lower a list of region tasks into the
+device tables of ``ug_fused_gemm`` (tensor maps, tasks, K segments, staged-copy
+pieces and their completion counters) and launch them.
+
+A *task* is one output region ``C[0:m, 0:n] (+)= sum_s A_s @ B_s``; every ``A_s``/``B_s``
+is a 2-D slice of some rank's tile.  Slices that live in this GPU's memory and
+satisfy the TMA alignment rules are read in place; remote slices (peer memory)
+and misaligned ones are *staged*: fetch warps inside the same kernel copy them
+into a local, aligned staging buffer and the TMA producer waits on per-chunk
+counters.  The order of the staged pieces follows the order in which the
+persistent CTAs will need them.
+
+The executors this replaces in the reference are host loops:
+stationary_c_plan.py:358-523 and stationary_b_plan.py:340-564.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import Callable, Sequence
+
+import numpy as np
+import torch
+
+from . import native
+from .native import BM, BN, BK
+
+_PIECE_BYTES = 32 * 1024
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+@dataclass(frozen=True)
+class OperandSlice:
+    """``rows x cols`` slice starting at ``(row0, col0)`` of a row-major tile.
+
+    ``base`` is the address, in this process, of element (0, 0) of the tile's
+    storage and ``ld`` its row pitch in elements.  ``remote`` marks memory of
+    another GPU (it is then never handed to TMA).
+    """
+
+    base: int
+    ld: int
+    row0: int
+    col0: int
+    rows: int
+    cols: int
+    remote: bool = False
+    elem_bytes: int = 2
+
+    def tma_ok(self) -> bool:
+        return (not self.remote) and self.base % 16 == 0 and (self.ld * self.elem_bytes) % 16 == 0 \
+            and (self.col0 * self.elem_bytes) % 16 == 0
+
+    def vector_ok(self) -> bool:
+        return self.base % 16 == 0 and (self.ld * self.elem_bytes) % 16 == 0 \
+            and (self.col0 * self.elem_bytes) % 16 == 0
+
+    def address(self, r: int = 0, c: int = 0) -> int:
+        return self.base + ((self.row0 + r) * self.ld + self.col0 + c) * self.elem_bytes
+
+
+@dataclass
+class TaskSpec:
+    c_ptr: int
+    ldc: int
+    m: int
+    n: int
+    c_mode: int
+    c_dtype: int
+    segments: list[tuple[OperandSlice, OperandSlice]] = field(default_factory=list)
+
+
+@dataclass
+class _Staged:
+    kind: str            # "a" (chunks of BM rows) or "b" (chunks of BN columns)
+    src: OperandSlice
+    offset: int          # byte offset into the staging buffer
+    ld: int              # elements
+    flag_base: int
+    num_chunks: int
+    map_index: int = -1
+
+
+class FusedProgram:
+    """Device-resident tables of one lowered plan, ready to launch."""
+
+    def __init__(self, *, device: torch.device, tables: torch.Tensor, staging: torch.Tensor | None,
+                 params: native.FusedParams, grid: int, clear_ptr: int, num_clear: int, stats: dict):
+        self.device = device
+        self._tables = tables
+        self._staging = staging
+        self.params = params
+        self.grid = grid
+        self.clear_ptr = clear_ptr
+        self.num_clear = num_clear
+        self.stats = stats
+
+    @property
+    def num_pieces(self) -> int:
+        return int(self.params.num_pieces)
+
+    def set_status_ptr(self, ptr: int) -> None:
+        self.params.status = ptr
+
+    def reset_flags(self, stream: int) -> None:
+        """Zero the chunk counters and the piece cursor (needed before every launch
+        when the program stages anything and no barrier kernel clears them)."""
+        if self.num_clear > 0:
+            native.check(native.lib().ug_zero_2d(self.clear_ptr, self.num_clear * 4, 1, self.num_clear * 4,
+                                                 ctypes.c_void_p(stream)), "ug_zero_2d(flags)")
+
+    def launch(self, stream: int) -> None:
+        native.check(native.lib().ug_fused_gemm(ctypes.byref(self.params), self.grid, ctypes.c_void_p(stream)),
+                     "ug_fused_gemm")
+
+
+class FusedProgramBuilder:
+    def __init__(self, device: torch.device, *, num_sms: int | None = None, timeout_ns: int = 4_000_000_000,
+                 range_check: Callable[[int, int, str], None] | None = None):
+        self.device = torch.device(device)
+        if num_sms is None:
+            num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.num_sms = int(num_sms)
+        self.timeout_ns = int(timeout_ns)
+        self.range_check = range_check
+        self.tasks: list[TaskSpec] = []
+
+    def add_task(self, task: TaskSpec) -> None:
+        if task.m <= 0 or task.n <= 0 or not task.segments:
+            return
+        for a, b in task.segments:
+            if a.rows != task.m or b.cols != task.n or a.cols != b.rows or a.cols <= 0:
+                raise ValueError(f"inconsistent segment shapes: A {a.rows}x{a.cols}, B {b.rows}x{b.cols}, "
+                                 f"C {task.m}x{task.n}")
+        self.tasks.append(task)
+
+    # ------------------------------------------------------------------ lowering
+    def build(self, status_ptr: int) -> FusedProgram:
+        dev = self.device
+        map_keys: dict[tuple, int] = {}
+        map_specs: list[tuple] = []
+
+        def add_map(base_or_offset, staged: bool, inner: int, outer: int, stride_bytes: int, box: tuple[int, int]) -> int:
+            key = (base_or_offset, staged, inner, outer, stride_bytes, box)
+            idx = map_keys.get(key)
+            if idx is None:
+                idx = len(map_specs)
+                map_keys[key] = idx
+                map_specs.append(key)
+            return idx
+
+        staged: dict[tuple, _Staged] = {}
+        staging_bytes = 0
+        num_flags = 0
+
+        def stage(kind: str, src: OperandSlice) -> _Staged:
+            nonlocal staging_bytes, num_flags
+            key = (kind, src)
+            st = staged.get(key)
+            if st is not None:
+                return st
+            ld = _round_up(src.cols, 64)
+            nbytes = _round_up(src.rows * ld * src.elem_bytes, 1024)
+            chunks = (src.rows + BM - 1) // BM if kind == "a" else (src.cols + BN - 1) // BN
+            st = _Staged(kind=kind, src=src, offset=staging_bytes, ld=ld, flag_base=num_flags, num_chunks=chunks)
+            staging_bytes += nbytes
+            num_flags += chunks
+            staged[key] = st
+            return st
+
+        # Pass 1: decide direct vs staged per operand and lay out tasks / segments.
+        seg_rows = []
+        task_rows = []
+        tile_begin = 0
+        seg_sources: list[tuple[_Staged | None, _Staged | None]] = []
+        for task in self.tasks:
+            m_tiles = (task.m + BM - 1) // BM
+            n_tiles = (task.n + BN - 1) // BN
+            seg_begin = len(seg_rows)
+            kblocks = 0
+            for a, b in task.segments:
+                row = dict(a_flag=-1, b_flag=-1, k_len=a.cols)
+                if a.tma_ok():
+                    row["a_map"] = add_map(a.base, False, a.col0 + a.cols, a.row0 + a.rows, a.ld * a.elem_bytes, (BK, BM))
+                    row["a_row0"], row["a_col0"] = a.row0, a.col0
+                    sa = None
+                else:
+                    sa = stage("a", a)
+                    sa.map_index = add_map(sa.offset, True, a.cols, a.rows, sa.ld * a.elem_bytes, (BK, BM))
+                    row["a_map"], row["a_row0"], row["a_col0"], row["a_flag"] = sa.map_index, 0, 0, sa.flag_base
+                if b.tma_ok():
+                    row["b_map"] = add_map(b.base, False, b.col0 + b.cols, b.row0 + b.rows, b.ld * b.elem_bytes, (64, BK))
+                    row["b_row0"], row["b_col0"] = b.row0, b.col0
+                    sb = None
+                else:
+                    sb = stage("b", b)
+                    sb.map_index = add_map(sb.offset, True, b.cols, b.rows, sb.ld * b.elem_bytes, (64, BK))
+                    row["b_map"], row["b_row0"], row["b_col0"], row["b_flag"] = sb.map_index, 0, 0, sb.flag_base
+                seg_rows.append(row)
+                seg_sources.append((sa, sb))
+                kblocks += (a.cols + BK - 1) // BK
+            c_elem = 4 if task.c_dtype == native.DT_F32 else 2
+            c_vec = int(task.c_ptr % 16 == 0 and (task.ldc * c_elem) % 16 == 0)
+            group_m = m_tiles if m_tiles <= 16 else 16
+            task_rows.append(dict(c_ptr=task.c_ptr, ldc=task.ldc, m=task.m, n=task.n, seg_begin=seg_begin,
+                                  seg_count=len(task.segments), tile_begin=tile_begin, m_tiles=m_tiles,
+                                  n_tiles=n_tiles, kblocks=kblocks, c_mode=task.c_mode, c_dtype=task.c_dtype,
+                                  c_vec=c_vec, group_m=group_m))
+            tile_begin += m_tiles * n_tiles
+        total_tiles = tile_begin
+        if len(map_specs) > 4096:
+            raise ValueError(f"plan needs {len(map_specs)} tensor maps (limit 4096)")
+
+        grid = self.num_sms if (staged or total_tiles >= self.num_sms) else max(total_tiles, 1)
+
+        # Pass 2: pieces of the staged copies, ordered by first use.
+        staging = None
+        staging_base = 0
+        if staging_bytes:
+            staging = torch.zeros(staging_bytes + 1024, dtype=torch.uint8, device=dev)
+            staging_base = _round_up(staging.data_ptr(), 1024)
+        pieces_by_chunk: dict[tuple[int, int], list[dict]] = {}
+        flag_need = np.zeros(max(num_flags, 1), dtype=np.int32)
+        for st in staged.values():
+            src = st.src
+            eb = src.elem_bytes
+            mode = 0 if src.vector_ok() else 1
+            for c in range(st.num_chunks):
+                plist = []
+                if st.kind == "a":
+                    r0, r1 = c * BM, min(src.rows, (c + 1) * BM)
+                    c0, c1 = 0, src.cols
+                else:
+                    r0, r1 = 0, src.rows
+                    c0, c1 = c * BN, min(src.cols, (c + 1) * BN)
+                row_bytes = (c1 - c0) * eb
+                rpp = max(1, _PIECE_BYTES // max(row_bytes, 1))
+                for r in range(r0, r1, rpp):
+                    rows = min(rpp, r1 - r)
+                    plist.append(dict(src=src.address(r, c0), dst=staging_base + st.offset + (r * st.ld + c0) * eb,
+                                      src_ld=src.ld * eb, dst_ld=st.ld * eb, rows=rows, row_bytes=row_bytes,
+                                      flag=st.flag_base + c, mode=mode))
+                    if self.range_check is not None:
+                        span = (rows - 1) * src.ld * eb + (_round_up(row_bytes, 16) if mode == 0 else row_bytes)
+                        self.range_check(src.address(r, c0), span, "staged source")
+                pieces_by_chunk[(id(st), c)] = plist
+                flag_need[st.flag_base + c] = len(plist)
+
+        ordered: list[dict] = []
+        if staged:
+            emitted: set[tuple[int, int]] = set()
+            # Tile order of the persistent grid: CTA b runs tiles b, b + grid, ...  All CTAs walk
+            # their K segments in order, so within a wave chunks are needed segment by segment.
+            coords = self._tile_coords(task_rows)
+            for wave_start in range(0, total_tiles, grid):
+                wave = coords[wave_start:wave_start + grid]
+                max_segs = max(task_rows[t]["seg_count"] for t, _, _ in wave)
+                for s in range(max_segs):
+                    for t, mt, nt in wave:
+                        tr = task_rows[t]
+                        if s >= tr["seg_count"]:
+                            continue
+                        sa, sb = seg_sources[tr["seg_begin"] + s]
+                        for st, ci in ((sa, mt), (sb, nt)):
+                            if st is None:
+                                continue
+                            key = (id(st), ci)
+                            if key not in emitted:
+                                emitted.add(key)
+                                ordered.extend(pieces_by_chunk[key])
+            for key, plist in pieces_by_chunk.items():   # chunks no tile asked for (cannot happen; keep counters sane)
+                if key not in emitted:
+                    ordered.extend(plist)
+
+        # Pass 3: pack tables into one device buffer.
+        seg_arr = np.zeros(max(len(seg_rows), 1), dtype=native.SEGMENT_DTYPE)
+        for i, row in enumerate(seg_rows):
+            for k, v in row.items():
+                seg_arr[i][k] = v
+        task_arr = np.zeros(max(len(task_rows), 1), dtype=native.TASK_DTYPE)
+        for i, row in enumerate(task_rows):
+            for k, v in row.items():
+                task_arr[i][k] = v
+        piece_arr = np.zeros(max(len(ordered), 1), dtype=native.PIECE_DTYPE)
+        for i, row in enumerate(ordered):
+            for k, v in row.items():
+                piece_arr[i][k] = v
+        maps_blob = bytearray()
+        for (base_or_off, is_staged, inner, outer, stride_bytes, box) in map_specs:
+            base = staging_base + base_or_off if is_staged else base_or_off
+            maps_blob += native.encode_tensor_map(base, native.DT_BF16, inner, outer, stride_bytes, box[0], box[1], 3)
+        if not maps_blob:
+            maps_blob = bytearray(128)
+
+        def pad(b: bytes, align: int = 256) -> bytes:
+            return b + bytes((-len(b)) % align)
+
+        sections = [pad(bytes(maps_blob)), pad(task_arr.tobytes()), pad(seg_arr.tobytes()), pad(piece_arr.tobytes()),
+                    pad(flag_need.tobytes()), pad(bytes(4 * (num_flags + 1)))]
+        offsets = np.cumsum([0] + [len(s) for s in sections])
+        blob = np.frombuffer(b"".join(sections), dtype=np.uint8).copy()
+        tables = torch.empty(len(blob) + 256, dtype=torch.uint8, device=dev)
+        base = _round_up(tables.data_ptr(), 256)
+        shift = base - tables.data_ptr()
+        tables[shift:shift + len(blob)].copy_(torch.from_numpy(blob))
+
+        params = native.FusedParams()
+        params.maps = base + int(offsets[0])
+        params.tasks = base + int(offsets[1])
+        params.segs = base + int(offsets[2])
+        params.pieces = base + int(offsets[3])
+        params.flag_need = base + int(offsets[4])
+        params.flags = base + int(offsets[5])
+        params.piece_counter = params.flags + 4 * num_flags
+        params.status = status_ptr
+        params.num_maps = len(map_specs)
+        params.num_tasks = len(task_rows)
+        params.num_pieces = len(ordered)
+        params.num_flags = num_flags
+        params.total_tiles = total_tiles
+        params.timeout_ns = self.timeout_ns
+        stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
+                     pieces=len(ordered), staged_bytes=staging_bytes,
+                     remote_bytes=sum(st.src.rows * st.src.cols * st.src.elem_bytes for st in staged.values()
+                                      if st.src.remote), grid=grid)
+        return FusedProgram(device=dev, tables=tables, staging=staging, params=params, grid=grid,
+                            clear_ptr=params.flags if staged else 0, num_clear=(num_flags + 1) if staged else 0,
+                            stats=stats)
+
+    @staticmethod
+    def _tile_coords(task_rows: Sequence[dict]) -> list[tuple[int, int, int]]:
+        """Linear tile index -> (task, m tile, n tile); mirrors ``locate`` in fused_gemm.cu."""
+        out: list[tuple[int, int, int]] = []
+        for t, tr in enumerate(task_rows):
+            m_tiles, n_tiles, gm = tr["m_tiles"], tr["n_tiles"], tr["group_m"]
+            for first_m in range(0, m_tiles, gm):
+                band_m = min(gm, m_tiles - first_m)
+                for nt in range(n_tiles):
+                    for i in range(band_m):
+                        out.append((t, first_m + i, nt))
+        return out
+
+
+def tile_coords_for_test(task_rows: Sequence[dict]) -> list[tuple[int, int, int]]:
+    return FusedProgramBuilder._tile_coords(task_rows)
