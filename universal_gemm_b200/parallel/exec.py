@@ -1,0 +1,261 @@
+"""Execution of Stationary-B / Stationary-C plans.
+
+Two executors:
+
+* **fused** (GPU, bf16 operands): the plan is grouped into output regions, lowered
+  once into the device tables of the persistent tcgen05 kernel (cached per matrix
+  triple) and every call is ``signal barrier -> fused kernel -> signal barrier`` on
+  the current stream.  Remote operand slices are pulled by the kernel's fetch
+  warps, partial C tiles of Stationary-B (and of replicated runs) are pushed into
+  the owner with ``red.add`` from the epilogue.  No host synchronisation.
+* **tilewise** (any device / dtype): one ``get_tile`` + matmul + ``accumulate_tile``
+  per op, the structure of the reference's executors
+  (stationary_c_plan.py:295-355, stationary_b_plan.py:267-337).  It is the CPU
+  path and the fp32 path.
+
+Signatures follow the reference's ``execute_stationary_{b,c}`` family
+(stationary_c_plan.py:526-581, stationary_b_plan.py:567-623); arguments that tuned
+its host loop (``max_outstanding_prefetch`` ...) are accepted and ignored by the
+fused executor.
+"""
+from __future__ import annotations
+
+from typing import Any, Sequence
+
+import torch
+
+from ..utils import profile
+from . import plan as P
+from . import runtime as R
+from . import tiles as T
+from .matrix import DistMatrix, resolve
+from .plan import MultiplyOp
+
+_program_cache: dict[tuple, Any] = {}
+
+
+def clear_program_cache() -> None:
+    _program_cache.clear()
+
+
+# ----------------------------------------------------------------------------- lowering
+def _owner(dm: DistMatrix, idx: tuple[int, int], replica: int | None = None) -> int:
+    return T.tile_rank(dm.layout, idx, replica=replica, rank=dm.rank)
+
+
+def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequence[MultiplyOp], *,
+               fuse_replica_reduce: bool = True, range_check: bool = True):
+    """Lower an op list into a :class:`~universal_gemm_b200.ops.fused.FusedProgram`."""
+    from ..ops import native
+    from ..ops.device import DeviceState, torch_dtype_code
+    from ..ops.fused import FusedProgramBuilder, OperandSlice, TaskSpec
+
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("the fused executor needs bfloat16 A and B")
+    state = DeviceState.get(c.device)
+    me = c.rank
+    rep_c = T.replication_factor(c.layout)
+    push_to_origin = fuse_replica_reduce and rep_c > 1
+
+    buffers = (a.buffer, b.buffer, c.buffer)
+
+    def check(ptr: int, nbytes: int, what: str) -> None:
+        if not any(buf.contains(ptr, nbytes) for buf in buffers):
+            raise RuntimeError(f"{what}: [{ptr:#x}, +{nbytes}) is outside the matrices' symmetric allocations")
+
+    builder = FusedProgramBuilder(c.device, num_sms=state.num_sms,
+                                  timeout_ns=getattr(c.world, "timeout_ns", 4_000_000_000),
+                                  range_check=check if range_check else None)
+    for region in P.group_ops(ops):
+        c_owner = _owner(c, region.c_idx, replica=0 if push_to_origin else None)
+        sl = region.c_slice
+        c_ptr = c.tile_ptr(c_owner) + (sl.rows.start * c.ld + sl.cols.start) * c.itemsize
+        m, n = sl.shape
+        if range_check:
+            check(c_ptr, ((m - 1) * c.ld + n) * c.itemsize, "C region")
+        if kind == "c" and not push_to_origin:
+            if c_owner != me:
+                raise RuntimeError(f"Stationary-C expects local c_idx={region.c_idx}, owner={c_owner}, rank={me}")
+            mode = native.C_ADD
+        else:
+            mode = native.C_ATOMIC
+        segs = []
+        for op in region.ops:
+            ao, bo = _owner(a, op.a_idx), _owner(b, op.b_idx)
+            if kind == "b" and bo != me:
+                raise RuntimeError(f"Stationary-B expects local b_idx={op.b_idx}, owner={bo}, rank={me}")
+            sa = OperandSlice(base=a.tile_ptr(ao), ld=a.ld, row0=op.a_slice.rows.start, col0=op.a_slice.cols.start,
+                              rows=op.a_slice.shape[0], cols=op.a_slice.shape[1], remote=ao != me)
+            sb = OperandSlice(base=b.tile_ptr(bo), ld=b.ld, row0=op.b_slice.rows.start, col0=op.b_slice.cols.start,
+                              rows=op.b_slice.shape[0], cols=op.b_slice.shape[1], remote=bo != me)
+            segs.append((sa, sb))
+        builder.add_task(TaskSpec(c_ptr=c_ptr, ldc=c.ld, m=m, n=n, c_mode=mode, c_dtype=torch_dtype_code(c.dtype),
+                                  segments=segs))
+    return builder.build(state.status_ptr)
+
+
+def _program(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequence[MultiplyOp], fuse: bool):
+    key = (kind, a.buffer.ptr(a.rank), b.buffer.ptr(b.rank), c.buffer.ptr(c.rank), c.rank, fuse)
+    hit = _program_cache.get(key)
+    if hit is not None and (hit[0] is ops or hit[0] == ops) and hit[1] == (a.layout, b.layout, c.layout):
+        return hit[2]
+    prog = lower_plan(kind, a, b, c, ops, fuse_replica_reduce=fuse)
+    _program_cache[key] = (ops, (a.layout, b.layout, c.layout), prog)
+    return prog
+
+
+def _can_fuse(a: DistMatrix, b: DistMatrix, c: DistMatrix) -> bool:
+    return (c.world.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+            and c.dtype in (torch.float32, torch.bfloat16))
+
+
+# ----------------------------------------------------------------------------- fused executor
+def _run_fused(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequence[MultiplyOp], *,
+               fuse_replica_reduce: bool = True, barriers: bool = True) -> None:
+    from ..ops.device import DeviceState
+
+    world = c.world
+    state = DeviceState.get(c.device)
+    prog = _program(kind, a, b, c, ops, fuse_replica_reduce)
+    prof = profile.enabled
+    if prof:
+        e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        e0.record()
+    # Entry barrier: every rank's operands (and zeroed C) are in place before any peer touches
+    # them; it also clears this plan's chunk counters.
+    if barriers or prog.num_clear:
+        if barriers:
+            world.device_barrier(prog.clear_ptr, prog.num_clear)
+        else:
+            state.zero_2d(prog.clear_ptr, prog.num_clear * 4, 1, prog.num_clear * 4)
+    if prof:
+        e1.record()
+    prog.launch(state.stream())
+    state.launches += 1
+    if prof:
+        e2.record()
+    # Exit barrier: all pushes into this rank's C have landed and peers are done reading A / B.
+    if barriers:
+        world.device_barrier()
+    if prof:
+        e3.record()
+        profile.record_events("comm_sync", e0, e1)
+        profile.record_events("compute", e1, e2)
+        profile.record_events("comm_sync", e2, e3)
+
+
+# ----------------------------------------------------------------------------- tilewise executor
+def _acc_dtype(dtype: torch.dtype) -> torch.dtype:
+    return torch.float32 if dtype in (torch.bfloat16, torch.float16) else dtype
+
+
+def _run_tilewise(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequence[MultiplyOp]) -> None:
+    """Region by region: fetch the needed slices, multiply with the library matmul, add into C.
+    Operand slices (not whole tiles) are fetched."""
+    me = c.rank
+    for region in P.group_ops(ops):
+        acc = None
+        for op in region.ops:
+            a_view = R.get_tile(a, op.a_idx, region=op.a_slice)
+            b_view = R.get_tile(b, op.b_idx, region=op.b_slice)
+            prod = torch.matmul(a_view.to(_acc_dtype(a.dtype)), b_view.to(_acc_dtype(b.dtype)))
+            acc = prod if acc is None else acc.add_(prod)
+            R.release_tile(a_view)
+            R.release_tile(b_view)
+        owner = _owner(c, region.c_idx)
+        if owner == me:
+            c_view = R.tile(c, region.c_idx)[region.c_slice.rows.as_slice(), region.c_slice.cols.as_slice()]
+            if kind == "c":
+                c_view.add_(acc.to(c.dtype))
+                continue
+        R.accumulate_tile(c, region.c_idx, acc.to(c.dtype), slice_=region.c_slice)
+
+
+# ----------------------------------------------------------------------------- entry points
+def _execute(kind: str, a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp] | None, *, local_only: bool,
+             executor: str | None, fuse_replica_reduce: bool, barriers: bool) -> list[MultiplyOp]:
+    a, b, c = resolve(a), resolve(b), resolve(c)
+    world = c.world
+    rep_c = T.replication_factor(c.layout)
+    if ops is None:
+        build = P.build_stationary_c_ops if kind == "c" else P.build_stationary_b_ops
+        ops = build(a.layout, b.layout, c.layout, local_only=local_only, rank=c.rank)
+    if executor is None:
+        executor = "fused" if _can_fuse(a, b, c) else "tilewise"
+    if executor == "fused":
+        if not _can_fuse(a, b, c):
+            raise RuntimeError("the fused executor needs a CUDA world and bfloat16 A / B")
+        if rep_c > 1 and not fuse_replica_reduce and T.my_replica(c.layout, c.rank) != 0:
+            c.local_padded.zero_()
+        _run_fused(kind, a, b, c, ops, fuse_replica_reduce=fuse_replica_reduce, barriers=barriers)
+        if rep_c > 1 and not fuse_replica_reduce:
+            R.reduce_replicas(c)
+            world.device_barrier()
+        return list(ops)
+    if executor != "tilewise":
+        raise ValueError(f"unknown executor {executor!r}")
+    if rep_c > 1 and T.my_replica(c.layout, c.rank) != 0:
+        # Partial results are reduced into replica 0; stale values of other replicas must not be re-added.
+        c.local_padded.zero_()
+    if barriers:
+        world.device_barrier()
+    _run_tilewise(kind, a, b, c, ops)
+    if barriers:
+        world.device_barrier()
+    if rep_c > 1:
+        R.reduce_replicas(c)
+        if barriers:
+            world.device_barrier()
+    return list(ops)
+
+
+def execute_stationary_c(a: Any, b: Any, c: Any, *, local_only: bool = True, release_remote_tiles: bool = True,
+                         use_async: bool | None = None, max_outstanding_prefetch: int = 1,
+                         executor: str | None = None, fuse_replica_reduce: bool = True,
+                         barriers: bool = True) -> list[MultiplyOp]:
+    """``C += A @ B`` with the owner of every C tile computing it.  Returns the op list."""
+    return _execute("c", a, b, c, None, local_only=local_only, executor=executor,
+                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers)
+
+
+def execute_stationary_b(a: Any, b: Any, c: Any, *, local_only: bool = True, release_remote_tiles: bool = True,
+                         use_async: bool | None = None, max_outstanding_prefetch: int = 1,
+                         max_outstanding_accumulates: int = 4, num_compute_streams: int = 2,
+                         executor: str | None = None, fuse_replica_reduce: bool = True,
+                         barriers: bool = True) -> list[MultiplyOp]:
+    """``C += A @ B`` with the owner of every B tile multiplying it and pushing partial C tiles."""
+    return _execute("b", a, b, c, None, local_only=local_only, executor=executor,
+                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers)
+
+
+def execute_stationary_c_ops(a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp], *, release_remote_tiles: bool = True,
+                             barriers: bool = True) -> None:
+    """Execute a given Stationary-C op list op by op (tilewise executor)."""
+    _execute("c", a, b, c, ops, local_only=True, executor="tilewise", fuse_replica_reduce=False, barriers=barriers)
+
+
+def execute_stationary_c_ops_async(a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp], *,
+                                   release_remote_tiles: bool = True, max_outstanding_prefetch: int = 1,
+                                   barriers: bool = True) -> None:
+    """Execute a given Stationary-C op list with the fused kernel when possible."""
+    _execute("c", a, b, c, ops, local_only=True, executor=None, fuse_replica_reduce=True, barriers=barriers)
+
+
+def execute_stationary_b_ops(a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp], *, release_remote_tiles: bool = True,
+                             barriers: bool = True) -> None:
+    _execute("b", a, b, c, ops, local_only=True, executor="tilewise", fuse_replica_reduce=False, barriers=barriers)
+
+
+def execute_stationary_b_ops_async(a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp], *,
+                                   release_remote_tiles: bool = True, max_outstanding_prefetch: int = 1,
+                                   max_outstanding_accumulates: int = 4, num_compute_streams: int = 2,
+                                   barriers: bool = True) -> None:
+    _execute("b", a, b, c, ops, local_only=True, executor=None, fuse_replica_reduce=True, barriers=barriers)
+
+
+def matmul(a: Any, b: Any, c: Any, *, method: str = "auto", **kwargs) -> list[MultiplyOp]:
+    """``C += A @ B`` with ``method`` in {auto, stationary_c, stationary_b}."""
+    chosen = P.select_method(method, resolve(b).layout, resolve(c).layout)
+    if chosen == "stationary_b":
+        return execute_stationary_b(a, b, c, **kwargs)
+    return execute_stationary_c(a, b, c, **kwargs)

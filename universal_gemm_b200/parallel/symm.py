@@ -1,0 +1,371 @@
+"""Symmetric memory: allocations of equal size on every rank that every rank of the
+node can address directly (one-sided loads, stores and atomics).
+
+Three interchangeable *worlds* provide it:
+
+* :class:`CudaIpcWorld` - one process per GPU; ``cudaMalloc`` + legacy CUDA IPC
+  handles exchanged through ``torch.distributed``.  Peer pointers are plain device
+  addresses the kernels dereference over NVLink.  No multicast object is created.
+* :class:`ShmWorld` - CPU ranks (``gloo``); allocations are files under ``/dev/shm``
+  mapped by every rank.  Used for the CPU configuration and the multi-process tests.
+* :class:`EmulatedCluster` - all ranks inside one process (CPU or one GPU), executed
+  one after the other.  The k-th allocation of every rank resolves to the k-th
+  allocation of the cluster, so code written for real worlds runs unchanged.
+
+This replaces the NVSHMEM symmetric heap and ``get_peer_tensor`` mappings of the
+reference (dtensor_scratch.py:9-53, dtensor_utils.py:30-115,546-552).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import uuid
+from typing import Sequence
+
+import torch
+
+_ALIGN = 1024
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class SymmBuffer:
+    """One collective allocation as seen from one rank."""
+
+    def __init__(self, world: "World", nbytes: int, ptrs: Sequence[int], tensors: Sequence[torch.Tensor | None],
+                 closer=None):
+        self.world = world
+        self.nbytes = int(nbytes)
+        self._ptrs = [int(p) for p in ptrs]
+        self._tensors = list(tensors)
+        self._closer = closer
+        self.closed = False
+
+    @property
+    def local(self) -> torch.Tensor:
+        t = self._tensors[self.world.rank]
+        assert t is not None
+        return t
+
+    def ptr(self, rank: int) -> int:
+        """Address of ``rank``'s copy, valid in this process (and on this GPU)."""
+        return self._ptrs[rank]
+
+    def tensor(self, rank: int) -> torch.Tensor | None:
+        """uint8 tensor over ``rank``'s copy when this world can express it (CPU, emulation, self)."""
+        return self._tensors[rank]
+
+    def contains(self, ptr: int, nbytes: int) -> bool:
+        return any(base <= ptr and ptr + nbytes <= base + self.nbytes for base in self._ptrs)
+
+    def free(self) -> None:
+        if not self.closed and self._closer is not None:
+            self._closer()
+        self.closed = True
+
+
+class World:
+    rank: int
+    size: int
+    device: torch.device
+    emulated = False
+
+    def alloc(self, nbytes: int) -> SymmBuffer:
+        raise NotImplementedError
+
+    def barrier(self) -> None:
+        """Host-level barrier across the ranks (collective)."""
+        raise NotImplementedError
+
+    def device_barrier(self, clear_ptr: int = 0, num_clear: int = 0) -> int:
+        """Stream-ordered barrier across the ranks; returns the number of kernels launched."""
+        raise NotImplementedError
+
+    @property
+    def is_cuda(self) -> bool:
+        return self.device.type == "cuda"
+
+    def close(self) -> None:
+        pass
+
+
+# ----------------------------------------------------------------------------- CUDA IPC
+class _CudaWrapper:
+    """Exposes a raw device allocation through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None,
+        }
+
+
+class CudaIpcWorld(World):
+    """One process per GPU of one node; symmetric allocations over CUDA IPC."""
+
+    def __init__(self, group=None, device: torch.device | None = None, timeout_s: float = 10.0):
+        import torch.distributed as dist
+        from ..ops import native
+        from ..ops.device import DeviceState
+
+        self._dist = dist
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = torch.device(device)
+        self._native = native
+        self.state = DeviceState.get(self.device)
+        self.timeout_ns = int(timeout_s * 1e9)
+        self._buffers: list[SymmBuffer] = []
+        # signal slots for the device barrier
+        self._signal = self.alloc(_ALIGN)
+        self._signal.local.zero_()
+        self._slots = torch.tensor([self._signal.ptr(r) for r in range(self.size)], dtype=torch.int64,
+                                   device=self.device)
+        self._seq = 0
+        torch.cuda.synchronize(self.device)
+        self.barrier()
+
+    def alloc(self, nbytes: int) -> SymmBuffer:
+        native, dist = self._native, self._dist
+        L = native.lib()
+        nbytes = _round_up(max(int(nbytes), 1), _ALIGN)
+        with torch.cuda.device(self.device):
+            ptr = ctypes.c_uint64(0)
+            native.check(L.ug_malloc(nbytes, ctypes.byref(ptr)), "ug_malloc")
+            handle = (ctypes.c_uint8 * 64)()
+            native.check(L.ug_ipc_get_handle(ptr.value, ctypes.cast(handle, ctypes.c_void_p)), "ug_ipc_get_handle")
+            mine = (bytes(handle), nbytes)
+            gathered: list = [None] * self.size
+            dist.all_gather_object(gathered, mine, group=self.group)
+            ptrs, opened = [], []
+            for r, (h, nb) in enumerate(gathered):
+                if nb != nbytes:
+                    raise RuntimeError(f"symmetric allocation size differs between ranks: {nb} vs {nbytes}")
+                if r == self.rank:
+                    ptrs.append(ptr.value)
+                    continue
+                peer = ctypes.c_uint64(0)
+                hb = (ctypes.c_uint8 * 64).from_buffer_copy(h)
+                native.check(L.ug_ipc_open(ctypes.cast(hb, ctypes.c_void_p), ctypes.byref(peer)), "ug_ipc_open")
+                ptrs.append(peer.value)
+                opened.append(peer.value)
+            local = torch.as_tensor(_CudaWrapper(ptr.value, nbytes), device=self.device)
+        tensors: list[torch.Tensor | None] = [None] * self.size
+        tensors[self.rank] = local
+
+        def closer(own=ptr.value, opened=tuple(opened)):
+            with torch.cuda.device(self.device):
+                for p in opened:
+                    L.ug_ipc_close(p)
+                L.ug_free(own)
+
+        buf = SymmBuffer(self, nbytes, ptrs, tensors, closer)
+        self._buffers.append(buf)
+        return buf
+
+    def barrier(self) -> None:
+        self._dist.barrier(group=self.group)
+
+    def device_barrier(self, clear_ptr: int = 0, num_clear: int = 0) -> int:
+        self._seq += 1
+        L = self._native.lib()
+        self._native.check(
+            L.ug_signal_barrier(self._slots.data_ptr(), self.size, self.rank, self._seq & 0xFFFFFFFF,
+                                self.state.status_ptr, self.timeout_ns, clear_ptr, num_clear,
+                                ctypes.c_void_p(self.state.stream())), "ug_signal_barrier")
+        self.state.launches += 1
+        return 1
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        self.barrier()
+        for buf in self._buffers:
+            buf.free()
+        self._buffers.clear()
+        self.barrier()
+
+
+# ----------------------------------------------------------------------------- CPU shared memory
+class ShmWorld(World):
+    """CPU ranks of one node; allocations are shared files under /dev/shm."""
+
+    def __init__(self, group=None, shm_dir: str = "/dev/shm"):
+        import torch.distributed as dist
+
+        self._dist = dist
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        self.device = torch.device("cpu")
+        self._dir = shm_dir
+        token = [uuid.uuid4().hex[:12] if self.rank == 0 else None]
+        dist.broadcast_object_list(token, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        self._token = token[0]
+        self._count = 0
+        self._paths: list[str] = []
+
+    def _path(self, index: int, rank: int) -> str:
+        return os.path.join(self._dir, f"ugemm_{self._token}_{index}_{rank}")
+
+    def alloc(self, nbytes: int) -> SymmBuffer:
+        nbytes = _round_up(max(int(nbytes), 1), _ALIGN)
+        index = self._count
+        self._count += 1
+        mine = self._path(index, self.rank)
+        with open(mine, "wb") as f:
+            f.truncate(nbytes)
+        self._paths.append(mine)
+        self._dist.barrier(group=self.group)
+        tensors = [torch.from_file(self._path(index, r), shared=True, size=nbytes, dtype=torch.uint8)
+                   for r in range(self.size)]
+        self._dist.barrier(group=self.group)
+        return SymmBuffer(self, nbytes, [t.data_ptr() for t in tensors], tensors, None)
+
+    def barrier(self) -> None:
+        self._dist.barrier(group=self.group)
+
+    def device_barrier(self, clear_ptr: int = 0, num_clear: int = 0) -> int:
+        self.barrier()
+        return 0
+
+    def lock_path(self, rank: int) -> str:
+        return os.path.join(self._dir, f"ugemm_{self._token}_lock_{rank}")
+
+    def close(self) -> None:
+        self.barrier()
+        for p in self._paths:
+            try:
+                os.unlink(p)
+            except OSError:
+                pass
+        self._paths.clear()
+        if self.rank == 0:
+            for r in range(self.size):
+                try:
+                    os.unlink(self.lock_path(r))
+                except OSError:
+                    pass
+
+
+# ----------------------------------------------------------------------------- emulation
+class EmulatedCluster:
+    """``size`` ranks inside this process.  ``cluster.world(r)`` is rank r's view."""
+
+    def __init__(self, size: int, device: torch.device | str = "cpu"):
+        self.size = int(size)
+        self.device = torch.device(device)
+        self._allocs: list[list[torch.Tensor]] = []
+        self._worlds = [EmulatedWorld(self, r) for r in range(self.size)]
+
+    def world(self, rank: int) -> "EmulatedWorld":
+        return self._worlds[rank]
+
+    def worlds(self) -> list["EmulatedWorld"]:
+        return list(self._worlds)
+
+    def _get(self, index: int, nbytes: int) -> list[torch.Tensor]:
+        if index == len(self._allocs):
+            self._allocs.append([torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+                                 for _ in range(self.size)])
+        tensors = self._allocs[index]
+        if tensors[0].numel() != nbytes:
+            raise RuntimeError("ranks of an emulated cluster must allocate in the same order and size")
+        return tensors
+
+
+class EmulatedWorld(World):
+    emulated = True
+
+    def __init__(self, cluster: EmulatedCluster, rank: int):
+        self.cluster = cluster
+        self.rank = rank
+        self.size = cluster.size
+        self.device = cluster.device
+        self._count = 0
+        self.timeout_ns = 4_000_000_000
+
+    def alloc(self, nbytes: int) -> SymmBuffer:
+        nbytes = _round_up(max(int(nbytes), 1), _ALIGN)
+        tensors = self.cluster._get(self._count, nbytes)
+        self._count += 1
+        return SymmBuffer(self, nbytes, [t.data_ptr() for t in tensors], tensors, None)
+
+    def barrier(self) -> None:
+        pass
+
+    def device_barrier(self, clear_ptr: int = 0, num_clear: int = 0) -> int:
+        # Ranks run one after the other, so only the local clearing part of the barrier remains.
+        if num_clear and self.is_cuda:
+            from ..ops.device import DeviceState
+
+            DeviceState.get(self.device).zero_2d(clear_ptr, num_clear * 4, 1, num_clear * 4)
+            return 1
+        return 0
+
+
+class SingleWorld(EmulatedWorld):
+    """A world of one rank (no peers); used on one GPU or one CPU process."""
+
+    def __init__(self, device: torch.device | str = "cpu"):
+        super().__init__(EmulatedCluster(1, device), 0)
+
+
+# ----------------------------------------------------------------------------- bump heap
+class SymmHeap:
+    """Bump allocator over one symmetric buffer (scratch for fetched tiles).
+
+    Like the reference heap (dtensor_scratch.py:9-53) it wraps around when full;
+    unlike it, it refuses to hand out memory that overlaps a view which is still
+    registered as live (``release`` ends a view's life).
+    """
+
+    def __init__(self, world: World, capacity_elements: int, dtype: torch.dtype):
+        if capacity_elements <= 0:
+            raise ValueError("capacity_elements must be positive")
+        self.world = world
+        self.dtype = dtype
+        self.itemsize = torch.empty(0, dtype=dtype).element_size()
+        self._capacity = int(capacity_elements)
+        self.buffer = world.alloc(self._capacity * self.itemsize)
+        self._cursor = 0
+        self._live: dict[int, tuple[int, int]] = {}
+
+    @property
+    def capacity(self) -> int:
+        return self._capacity
+
+    def reset(self) -> None:
+        self._cursor = 0
+        self._live.clear()
+
+    def alloc(self, shape: Sequence[int]) -> torch.Tensor:
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        if numel == 0:
+            return self.buffer.local[:0].view(self.dtype).view(*shape)
+        step = _round_up(numel, max(1, 256 // self.itemsize))     # keep every view 256-byte aligned
+        if numel > self._capacity:
+            raise RuntimeError(f"SymmHeap exhausted: requested={numel} elements, capacity={self._capacity} elements")
+        start = self._cursor
+        if start + numel > self._capacity:
+            start = 0
+        end = start + numel
+        for lo, hi in self._live.values():
+            if lo < end and start < hi:
+                raise RuntimeError("SymmHeap wrapped onto a tile that is still in use; release tiles or grow the heap")
+        view = self.buffer.local[start * self.itemsize:end * self.itemsize].view(self.dtype).view(*shape)
+        self._live[view.data_ptr()] = (start, end)
+        self._cursor = min(start + step, self._capacity)
+        return view
+
+    def release(self, view: torch.Tensor) -> None:
+        self._live.pop(view.data_ptr(), None)
+
+    def close(self) -> None:
+        self._live.clear()
+        self.buffer.free()
