@@ -1,0 +1,188 @@
+#!/usr/bin/env python3
+"""Headline benchmark: whole-box TFLOP/s of one distributed GEMM ``C = A @ B``.
+
+Default configuration: the GPT-3-175B MLP up-projection, A = [8192, 12288] activations,
+B = [12288, 49152] weights, bf16 inputs with fp32 accumulation and fp32 C, partition triple
+row / column / row, replication 1, method ``auto``; random-init synthetic data.  The total
+problem is fixed, so the scaling over 1 / 2 / 4 / 8 GPUs is strong scaling.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+One step = zero C + distributed GEMM (entry barrier, fused tcgen05 kernel with in-kernel tile
+fetch / remote accumulate, exit barrier).  ``value`` is 2*M*N*K / (device time per step, max
+over ranks).  ``e2e`` repeats the measurement through the same public call but with, every
+step, the host-to-device copy of that step's activations from pinned memory and a
+device-to-host read of a checksum of the result, synchronising the host each step.
+
+``--impl reference`` runs the unmodified reference benchmark worker instead (see baseline/).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=49152)
+    ap.add_argument("--k", type=int, default=12288)
+    ap.add_argument("--a-partition", default="row")
+    ap.add_argument("--b-partition", default="column")
+    ap.add_argument("--c-partition", default="row")
+    ap.add_argument("--replication", type=int, default=1)
+    ap.add_argument("--method", default="auto", choices=["auto", "stationary_c", "stationary_b"])
+    ap.add_argument("--c-dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--master-port", type=int, default=29517)
+    return ap.parse_args(argv)
+
+
+def _relaunch_under_torchrun(args) -> int:
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+           "--master-addr", "127.0.0.1", "--master-port", str(args.master_port), os.path.abspath(__file__)] + sys.argv[1:]
+    return subprocess.call(cmd)
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    import universal_gemm_b200 as ug
+    from universal_gemm_b200.ops.device import DeviceState
+    from universal_gemm_b200.utils.benchmarking import ClockSampler, max_over_ranks, sync_all
+
+    world = ug.init()
+    if not world.is_cuda:
+        raise RuntimeError("bench.py needs a CUDA device")
+    if world.size != args.gpus:
+        raise RuntimeError(f"--gpus {args.gpus} but the launcher started {world.size} rank(s)")
+    dev = world.device
+    state = DeviceState.get(dev)
+    m, n, k = args.m, args.n, args.k
+    c_dtype = torch.float32 if args.c_dtype == "fp32" else torch.bfloat16
+
+    a = ug.empty(world, (m, k), args.a_partition, torch.bfloat16, args.replication)
+    b = ug.empty(world, (k, n), args.b_partition, torch.bfloat16, args.replication)
+    c = ug.zeros(world, (m, n), args.c_partition, c_dtype, args.replication)
+    g = torch.Generator(device=dev).manual_seed(20260218 + world.rank)
+    a.local_padded.zero_()
+    b.local_padded.zero_()
+    a.local.copy_(torch.randn(a.local.shape, generator=g, device=dev) * 0.02)
+    b.local.copy_(torch.randn(b.local.shape, generator=g, device=dev) * 0.02)
+    method = ug.select_method(args.method, b.layout, c.layout)
+
+    def step():
+        state.zero_2d(c.local_padded.data_ptr(), c.ld * c.itemsize, c.local_padded.shape[0], c.ld * c.itemsize)
+        ug.matmul(a, b, c, method=method)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync_all(world)
+    ug.check_status(dev)
+
+    sampler = ClockSampler(dev.index or 0) if world.rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = state.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all(world)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync_all(world)
+    ms_per_step = max_over_ranks(e0.elapsed_time(e1) / args.steps, dev)
+    launches = state.launches - launches0
+    ug.check_status(dev)
+
+    # End to end: pinned host activations -> device every step, checksum of C -> host every step.
+    e2e = None
+    if not args.no_e2e:
+        host_a = torch.empty(a.local.shape, dtype=torch.bfloat16).pin_memory()
+        host_a.copy_(a.local)
+        host_out = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            a.local.copy_(host_a, non_blocking=True)
+            step()
+            host_out.copy_(c.local.sum(dtype=torch.float32).reshape(1), non_blocking=True)
+            torch.cuda.current_stream(dev).synchronize()
+            return float(host_out[0])
+
+        for _ in range(3):
+            e2e_step()
+        sync_all(world)
+        t0 = time.perf_counter()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        s1.record()
+        sync_all(world)
+        wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        e2e_ms = max_over_ranks(max(s0.elapsed_time(s1) / args.steps, 0.0), dev)
+        e2e = {"value": 2.0 * m * n * k / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+               "host_wall_ms_per_step": wall_ms,
+               "h2d_bytes_per_step": host_a.numel() * host_a.element_size() * world.size,
+               "d2h_bytes_per_step": 4 * world.size}
+    clocks = sampler.stop() if sampler else None
+    ug.check_status(dev)
+
+    flops = 2.0 * m * n * k
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    shard_bytes = min(a.nbytes, b.nbytes, c.nbytes)
+    result = {
+        "metric": "whole-box TFLOP/s (2*M*N*K / device time, max over ranks)",
+        "value": value, "unit": "TFLOP/s", "n_gpus": world.size, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init N(0, 0.02) weights and activations)",
+        "impl": "ours", "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
+        "config": {"model": "GPT-3-175B MLP up-projection GEMM" if (n, k) == (49152, 12288) else "GEMM",
+                   "m": m, "n": n, "k": k, "global_batch": m, "seq_len": None,
+                   "parallelism": f"{args.a_partition},{args.b_partition},{args.c_partition} rep{args.replication} "
+                                  f"{method} x{world.size}",
+                   "c_dtype": args.c_dtype, "accumulate": "fp32 (TMEM)",
+                   "l2": f"inputs larger than L2 (B shard {b.nbytes >> 20} MiB, C shard {c.nbytes >> 20} MiB per rank)"
+                         if max(a.nbytes, b.nbytes, c.nbytes) > 126 * 2 ** 20 else
+                         f"smallest shard {shard_bytes >> 20} MiB; C is rewritten every step",
+                   "step": "zero C + barrier + fused GEMM + barrier"},
+    }
+    rank = world.rank
+    world.close()
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+def main(argv=None) -> int:
+    args = parse_args(argv)
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(REPO, "baseline"))
+        import run_reference
+
+        return run_reference.main(args)
+    if args.gpus > 1 and "RANK" not in os.environ:
+        return _relaunch_under_torchrun(args)
+    result = run_ours(args)
+    if result:
+        print(json.dumps(result), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

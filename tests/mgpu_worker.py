@@ -1,0 +1,89 @@
+"""Multi-process worker for the multi-GPU (or multi-process CPU) tests.
+
+Launched by ``torch.distributed.run`` with one rank per GPU (``--device cuda``) or as gloo
+ranks on CPU (``--device cpu``).  Every rank builds the same full matrices from a seed,
+distributes them into symmetric memory, runs the requested methods and compares the gathered
+result against an fp64 oracle.  Exit code 0 means every case passed on every rank.
+"""
+from __future__ import annotations
+
+import argparse
+import itertools
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import universal_gemm_b200 as ug  # noqa: E402
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--device", default="cuda")
+    ap.add_argument("--cases", default="small")
+    args = ap.parse_args()
+    world = ug.init(device=args.device)
+    dev = world.device
+    in_dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    rank, size = world.rank, world.size
+    parts = ("row", "column", "block")
+    if args.cases == "small":
+        shapes = [(301, 203, 157)]
+        triples = list(itertools.product(parts, repeat=3))
+        reps = [r for r in (1, 2) if size % r == 0]
+    elif args.cases == "tiny":
+        shapes = [(64, 48, 40)]
+        triples = [("row", "row", "row"), ("row", "column", "row"), ("column", "row", "row"), ("block", "block", "block")]
+        reps = [r for r in (1, 2) if size % r == 0]
+    else:
+        shapes = [(2048, 3072, 4096)]
+        triples = [("row", "row", "row"), ("row", "column", "row"), ("column", "row", "row"), ("block", "block", "block")]
+        reps = [r for r in (1, 2) if size % r == 0]
+    failures = 0
+    ncases = 0
+    for (m, n, k), triple, rep, method in itertools.product(shapes, triples, reps, ("stationary_c", "stationary_b")):
+        g = torch.Generator().manual_seed(1234 + m + n + k)
+        full_a = torch.randn(m, k, generator=g).to(dev)
+        full_b = (torch.randn(k, n, generator=g) / k ** 0.5).to(dev)
+        full_c = torch.randn(m, n, generator=g).to(dev)
+        a = ug.distribute_tensor(full_a, world, triple[0], rep, dtype=in_dtype)
+        b = ug.distribute_tensor(full_b, world, triple[1], rep, dtype=in_dtype)
+        c = ug.distribute_tensor(full_c, world, triple[2], rep, dtype=torch.float32)
+        iters = 2
+        for _ in range(iters):
+            ug.matmul(a, b, c, method=method)
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+            try:
+                ug.check_status(dev)
+            except Exception as exc:  # noqa: BLE001
+                print(f"[rank {rank}] status error in {triple} rep={rep} {method}: {exc}", flush=True)
+                failures += 1
+        world.barrier()
+        got = c.full_tensor(replica=0).double()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        want = full_c.double() + iters * (full_a.to(in_dtype).double() @ full_b.to(in_dtype).double())
+        err = (got - want).abs().max().item()
+        ok = err <= 3e-3 * max(1.0, want.abs().max().item())
+        ncases += 1
+        if not ok:
+            failures += 1
+            print(f"[rank {rank}] FAIL {m}x{n}x{k} {triple} rep={rep} {method}: max err {err:.3e}", flush=True)
+        world.barrier()
+        for mat in (a, b, c):
+            mat.free()
+    t = torch.tensor([failures], device=dev, dtype=torch.int64)
+    dist.all_reduce(t)
+    if rank == 0:
+        print(f"mgpu_worker: world={size} device={dev.type} cases={ncases} failures={int(t.item())}", flush=True)
+    world.close()
+    dist.destroy_process_group()
+    return 1 if int(t.item()) else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

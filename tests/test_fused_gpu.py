@@ -1,0 +1,210 @@
+"""GPU tests: the fused tcgen05 kernel and the tile kernels against fp32 PyTorch references,
+and the fused executors on an emulated multi-rank cluster that lives on one GPU (ranks run
+one after the other; remote tiles are other buffers of the same GPU, so every fetch / push
+path of the kernel is exercised without a second device)."""
+import pytest
+import torch
+
+import universal_gemm_b200 as ug
+
+from helpers import ALL_TRIPLES, build_cluster_matrices, make_inputs, oracle, run_cluster
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _status_ok():
+    from universal_gemm_b200.ops.device import DeviceState
+
+    torch.cuda.synchronize()
+    DeviceState.get(_dev()).check()
+
+
+def _native_loaded():
+    from universal_gemm_b200.ops import build
+
+    with open("/proc/self/maps") as f:
+        return str(build.library_path()) in f.read()
+
+
+def test_native_library_is_loaded():
+    from universal_gemm_b200.ops import native
+
+    assert native.lib().ug_version() >= 1
+    assert _native_loaded()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (512, 1024, 512), (300, 520, 200), (375, 1000, 376),
+                                   (64, 4099, 1024), (2048, 4096, 1024), (1, 8, 8)])
+@pytest.mark.parametrize("mode", ["store", "add", "atomic"])
+def test_gemm_kernel_fp32_out(m, n, k, mode):
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.gemm import gemm
+
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k, device=_dev()).bfloat16()
+    b = (torch.randn(k, n, device=_dev()) / k ** 0.5).bfloat16()
+    c0 = torch.randn(m, n, device=_dev())
+    c = c0.clone()
+    gemm(a, b, c, mode={"store": native.C_STORE, "add": native.C_ADD, "atomic": native.C_ATOMIC}[mode])
+    _status_ok()
+    ref = a.float() @ b.float() + (0 if mode == "store" else c0)
+    torch.testing.assert_close(c, ref, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("mode", ["store", "add", "atomic"])
+def test_gemm_kernel_bf16_out(mode):
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.gemm import gemm
+
+    torch.manual_seed(5)
+    m, n, k = 384, 777, 320
+    a = torch.randn(m, k, device=_dev()).bfloat16()
+    b = (torch.randn(k, n, device=_dev()) / k ** 0.5).bfloat16()
+    c0 = torch.randn(m, n, device=_dev()).bfloat16()
+    c = c0.clone()
+    gemm(a, b, c, mode={"store": native.C_STORE, "add": native.C_ADD, "atomic": native.C_ATOMIC}[mode])
+    _status_ok()
+    ref = a.float() @ b.float() + (0 if mode == "store" else c0.float())
+    torch.testing.assert_close(c.float(), ref, rtol=2e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("stage_a,stage_b", [(True, False), (False, True), (True, True)])
+def test_gemm_kernel_segments_and_staging(stage_a, stage_b):
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.gemm import build_gemm_program, run_program
+
+    torch.manual_seed(9)
+    m, n, k = 640, 1290, 1500
+    a = torch.randn(m, k, device=_dev()).bfloat16()
+    b = (torch.randn(k, n, device=_dev()) / k ** 0.5).bfloat16()
+    c = torch.zeros(m, n, device=_dev())
+    cuts = [0, 500, 1001, 1500]          # 1001 is not a multiple of 8: that segment is staged and re-aligned
+    prog = build_gemm_program([a[:, cuts[i]:cuts[i + 1]] for i in range(3)], [b[cuts[i]:cuts[i + 1]] for i in range(3)],
+                              c, mode=native.C_STORE, stage_a=stage_a, stage_b=stage_b)
+    assert prog.num_pieces > 0
+    for _ in range(2):                   # second launch checks that the counters are reset
+        run_program(prog, _dev())
+    _status_ok()
+    torch.testing.assert_close(c, a.float() @ b.float(), rtol=2e-3, atol=2e-3)
+
+
+def test_tile_kernels():
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.device import DeviceState
+
+    st = DeviceState.get(_dev())
+    torch.manual_seed(0)
+    for dtype, code in ((torch.float32, native.DT_F32), (torch.bfloat16, native.DT_BF16)):
+        es = torch.empty(0, dtype=dtype).element_size()
+        for rows, cols, off in ((64, 128, 0), (37, 53, 0), (37, 53, 3), (1, 8, 0)):
+            src = torch.randn(rows + 2, cols + 16, device=_dev()).to(dtype)
+            dst = torch.zeros(rows + 2, cols + 24, device=_dev(), dtype=dtype)
+            sv, dv = src[1:1 + rows, off:off + cols], dst[1:1 + rows, 8:8 + cols]
+            st.pull_2d(dv.data_ptr(), dst.stride(0) * es, sv.data_ptr(), src.stride(0) * es, rows, cols * es, es)
+            torch.cuda.synchronize()
+            outside = dst.clone()
+            outside[1:1 + rows, 8:8 + cols] = 0
+            assert torch.equal(dv, sv) and outside.abs().max().item() == 0
+            before = dv.clone()
+            st.accumulate_2d(dv.data_ptr(), dst.stride(0), sv.data_ptr(), src.stride(0), rows, cols, code)
+            torch.cuda.synchronize()
+            torch.testing.assert_close(dv.float(), before.float() * 2, rtol=1e-2, atol=1e-2)
+            st.zero_2d(dv.data_ptr(), dst.stride(0) * es, rows, cols * es)
+            torch.cuda.synchronize()
+            assert dst.abs().sum() == 0
+    f = torch.randn(33, 47, device=_dev())
+    h = torch.zeros(33, 64, device=_dev(), dtype=torch.bfloat16)
+    st.convert_2d(h.data_ptr(), 64, native.DT_BF16, f.data_ptr(), 47, native.DT_F32, 33, 47)
+    torch.cuda.synchronize()
+    assert torch.equal(h[:, :47], f.bfloat16())
+
+
+@pytest.mark.parametrize("world,rep", [(1, 1), (2, 1), (4, 2), (8, 1), (8, 2), (8, 4)])
+@pytest.mark.parametrize("method", ["stationary_c", "stationary_b"])
+def test_fused_all_triples_emulated(world, rep, method):
+    m, n, k = 301, 203, 157
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=world + rep, device=_dev())
+    triples = ALL_TRIPLES if world == 8 and rep == 1 else ALL_TRIPLES[::3]
+    for triple in triples:
+        cluster = ug.EmulatedCluster(world, _dev())
+        mats = build_cluster_matrices(cluster, full_a, full_b, full_c, triple, rep, torch.bfloat16, torch.float32)
+        run_cluster(cluster, mats, method, executor="fused")
+        _status_ok()
+        got = mats[0][2].full_tensor(replica=0)
+        torch.testing.assert_close(got.double(), oracle(full_a, full_b, full_c, torch.bfloat16), rtol=2e-3, atol=2e-3,
+                                   msg=lambda s: f"{method} {triple} world={world} rep={rep}: {s}")
+
+
+@pytest.mark.parametrize("triple", [("row", "row", "row"), ("row", "column", "row"), ("column", "row", "row"),
+                                    ("block", "block", "block")])
+@pytest.mark.parametrize("method", ["stationary_c", "stationary_b", "auto"])
+def test_fused_medium_shapes_emulated(triple, method):
+    m, n, k = 1024, 1536, 2048
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=11, device=_dev())
+    for rep, out_dtype in ((1, torch.float32), (2, torch.float32), (1, torch.bfloat16)):
+        cluster = ug.EmulatedCluster(8, _dev())
+        mats = build_cluster_matrices(cluster, full_a, full_b, full_c, triple, rep, torch.bfloat16, out_dtype)
+        for _ in range(2):
+            run_cluster(cluster, mats, method, executor="fused")
+        _status_ok()
+        got = mats[0][2].full_tensor(replica=0).double()
+        want = full_c.to(out_dtype).double() + 2 * (full_a.bfloat16().double() @ full_b.bfloat16().double())
+        tol = 3e-3 if out_dtype == torch.float32 else 6e-2
+        torch.testing.assert_close(got, want, rtol=tol, atol=tol,
+                                   msg=lambda s: f"{method} {triple} rep={rep} {out_dtype}: {s}")
+
+
+def test_unfused_replica_reduce_and_tilewise_on_gpu():
+    m, n, k = 256, 320, 512
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=2, device=_dev())
+    for executor in ("fused", "tilewise"):
+        cluster = ug.EmulatedCluster(4, _dev())
+        mats = build_cluster_matrices(cluster, full_a, full_b, full_c, ("row", "row", "row"), 2, torch.bfloat16,
+                                      torch.float32)
+        run_cluster(cluster, mats, "stationary_c", executor=executor, fuse_replica_reduce=False)
+        _status_ok()
+        torch.testing.assert_close(mats[0][2].full_tensor().double(), oracle(full_a, full_b, full_c, torch.bfloat16),
+                                   rtol=3e-3, atol=3e-3)
+
+
+def test_tile_api_on_gpu():
+    cluster = ug.EmulatedCluster(4, _dev())
+    full = torch.randn(64, 48, device=_dev())
+    mats = [ug.distribute_tensor(full, w, "row") for w in cluster.worlds()]
+    dm = mats[1]
+    ug.init_scratch(4 * 16 * 64, torch.float32, world=dm.world)
+    t = ug.get_tile(dm, (3, 0))
+    fut = ug.get_tile_async(dm, (0, 0), region=ug.Slice2D(ug.Slice1D(3, 9), ug.Slice1D(5, 40)))
+    part = fut.get()
+    torch.cuda.synchronize()
+    assert torch.equal(t, full[48:64]) and torch.equal(part, full[3:9, 5:40])
+    ug.release_tile(t)
+    ug.accumulate_tile(dm, (2, 0), torch.ones(16, 48, device=_dev())).wait()
+    torch.testing.assert_close(mats[2].local, full[32:48] + 1)
+    ug.free_get_tile_scratch()
+
+
+def test_bounded_wait_reports_timeout_instead_of_hanging():
+    """A cross-rank barrier whose peer never signals runs out after its limit and reports a
+    status code; the context stays usable."""
+    import ctypes
+
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.device import DeviceState, KernelStatusError
+
+    st = DeviceState.get(_dev())
+    slots = torch.zeros(2, 8, dtype=torch.int32, device=_dev())      # "rank 1" never adds to our slot
+    table = torch.tensor([slots[0].data_ptr(), slots[1].data_ptr()], dtype=torch.int64, device=_dev())
+    native.check(native.lib().ug_signal_barrier(table.data_ptr(), 2, 0, 1, st.status_ptr, 50_000_000, 0, 0,
+                                                ctypes.c_void_p(st.stream())), "ug_signal_barrier")
+    torch.cuda.synchronize()
+    with pytest.raises(KernelStatusError) as err:
+        st.check()
+    assert err.value.code == native.ERR_TIMEOUT_PEER
+    assert slots[1, 0].item() == 1                                    # our own signal was delivered
+    st.check()                                                        # status cleared, context alive
+    assert torch.ones(4, device=_dev()).sum().item() == 4

@@ -1,0 +1,37 @@
+"""Real multi-process runs: gloo ranks on CPU (shared-memory world) here, one rank per GPU on
+a multi-GPU box."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mgpu_worker.py")
+
+
+def _launch(nproc, device, cases, port, timeout=900, extra_env=None):
+    env = dict(os.environ)
+    env.update({"MASTER_ADDR": "127.0.0.1", "OMP_NUM_THREADS": "2"})
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), WORKER, "--device", device, "--cases", cases]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_cpu_gloo_shared_memory_world(nproc):
+    proc = _launch(nproc, "cpu", "tiny", 29610 + nproc)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "failures=0" in proc.stdout
+
+
+@pytest.mark.gpu
+def test_multi_gpu_ipc_world():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    nproc = 8 if n >= 8 else 4 if n >= 4 else 2
+    proc = _launch(nproc, "cuda", "small", 29650, extra_env={"NCCL_NVLS_ENABLE": "0"})
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "failures=0" in proc.stdout
