@@ -20,6 +20,8 @@ class _Unavailable:
         raise RuntimeError(f"{self._name} is not available on this image (nvshmem4py / cuda.core are not installed)")
 
     def __getattr__(self, item):
+        if item.startswith("__"):
+            raise AttributeError(item)
         return _Unavailable(f"{self._name}.{item}")
 
 
@@ -30,7 +32,13 @@ def install() -> None:
         nv_types = types.ModuleType("nvshmem.core.nvshmem_types")
         nv_types.NvshmemStream = object
         core.nvshmem_types = nv_types
-        core.__getattr__ = lambda name: _Unavailable(f"nvshmem.core.{name}")  # type: ignore[attr-defined]
+
+        def _core_getattr(name: str):
+            if name.startswith("__"):
+                raise AttributeError(name)
+            return _Unavailable(f"nvshmem.core.{name}")
+
+        core.__getattr__ = _core_getattr  # type: ignore[attr-defined]
         nv.core = core
         sys.modules.update({"nvshmem": nv, "nvshmem.core": core, "nvshmem.core.nvshmem_types": nv_types})
     try:
