@@ -36,6 +36,7 @@ def main() -> None:
     ap.add_argument("--mode", choices=["store", "add", "atomic"], default="store")
     ap.add_argument("--c-dtype", choices=["fp32", "bf16"], default="fp32")
     ap.add_argument("--no-torch", action="store_true")
+    ap.add_argument("--tile-m", type=int, choices=[128, 256], default=None, help="rows per output tile (default: model)")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     m, n, k = args.m, args.n, args.k
@@ -46,7 +47,7 @@ def main() -> None:
     mode = {"store": native.C_STORE, "add": native.C_ADD, "atomic": native.C_ATOMIC}[args.mode]
     prog = build_gemm_program([a[:, cuts[i]:cuts[i + 1]] for i in range(args.segments)],
                               [b[cuts[i]:cuts[i + 1]] for i in range(args.segments)], c, mode=mode,
-                              stage_a=args.stage_a, stage_b=args.stage_b)
+                              stage_a=args.stage_a, stage_b=args.stage_b, tile_m=args.tile_m)
 
     def timed(fn):
         for _ in range(args.warmup):

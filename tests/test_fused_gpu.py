@@ -40,7 +40,8 @@ def test_native_library_is_loaded():
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (512, 1024, 512), (300, 520, 200), (375, 1000, 376),
                                    (64, 4099, 1024), (2048, 4096, 1024), (1, 8, 8)])
 @pytest.mark.parametrize("mode", ["store", "add", "atomic"])
-def test_gemm_kernel_fp32_out(m, n, k, mode):
+@pytest.mark.parametrize("tile_m", [128, 256])
+def test_gemm_kernel_fp32_out(m, n, k, mode, tile_m):
     from universal_gemm_b200.ops import native
     from universal_gemm_b200.ops.gemm import gemm
 
@@ -49,7 +50,7 @@ def test_gemm_kernel_fp32_out(m, n, k, mode):
     b = (torch.randn(k, n, device=_dev()) / k ** 0.5).bfloat16()
     c0 = torch.randn(m, n, device=_dev())
     c = c0.clone()
-    gemm(a, b, c, mode={"store": native.C_STORE, "add": native.C_ADD, "atomic": native.C_ATOMIC}[mode])
+    gemm(a, b, c, mode={"store": native.C_STORE, "add": native.C_ADD, "atomic": native.C_ATOMIC}[mode], tile_m=tile_m)
     _status_ok()
     ref = a.float() @ b.float() + (0 if mode == "store" else c0)
     torch.testing.assert_close(c, ref, rtol=2e-3, atol=2e-3)
@@ -73,7 +74,8 @@ def test_gemm_kernel_bf16_out(mode):
 
 
 @pytest.mark.parametrize("stage_a,stage_b", [(True, False), (False, True), (True, True)])
-def test_gemm_kernel_segments_and_staging(stage_a, stage_b):
+@pytest.mark.parametrize("tile_m", [128, 256])
+def test_gemm_kernel_segments_and_staging(stage_a, stage_b, tile_m):
     from universal_gemm_b200.ops import native
     from universal_gemm_b200.ops.gemm import build_gemm_program, run_program
 
@@ -84,7 +86,7 @@ def test_gemm_kernel_segments_and_staging(stage_a, stage_b):
     c = torch.zeros(m, n, device=_dev())
     cuts = [0, 500, 1001, 1500]          # 1001 is not a multiple of 8: that segment is staged and re-aligned
     prog = build_gemm_program([a[:, cuts[i]:cuts[i + 1]] for i in range(3)], [b[cuts[i]:cuts[i + 1]] for i in range(3)],
-                              c, mode=native.C_STORE, stage_a=stage_a, stage_b=stage_b)
+                              c, mode=native.C_STORE, stage_a=stage_a, stage_b=stage_b, tile_m=tile_m)
     assert prog.num_pieces > 0
     for _ in range(2):                   # second launch checks that the counters are reset
         run_program(prog, _dev())

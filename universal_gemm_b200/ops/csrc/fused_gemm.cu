@@ -40,13 +40,28 @@ constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
 constexpr int kFetchWarp0 = 6;  // warps 2..5 are the epilogue, 6..9 fetch
 
-constexpr uint32_t kABytes = UG_BM * UG_BK * 2;        // 16 KiB
 constexpr uint32_t kBChunkBytes = UG_BK * 64 * 2;      // 8 KiB: 64 k rows x 64 n elements
 constexpr uint32_t kBBytes = 4 * kBChunkBytes;         // 32 KiB
-constexpr uint32_t kStageBytes = kABytes + kBBytes;    // 48 KiB
-constexpr uint32_t kRingBytes = UG_STAGES * kStageBytes;
-constexpr uint32_t kTmemCols = 512;                    // two 128x256 fp32 accumulators
-constexpr uint32_t kSmemBytes = kRingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t kEpiRowFloats = 36;                 // 32 columns + 4 of padding: conflict-free v4 rows
+constexpr uint32_t kEpiWarpBytes = 32 * kEpiRowFloats * 4;
+constexpr uint32_t kEpiBytes = 4 * kEpiWarpBytes;      // one transpose buffer per epilogue warp
+constexpr uint32_t kTmemCols = 512;                    // 128 lanes x 512 fp32 columns: all of TMEM
+
+// Two tile shapes share the kernel source:
+//   BM = 128: tile 128 x 256, 4 stages of 48 KiB, two accumulators (epilogue overlaps the next main loop);
+//             96 operand bytes per tensor cycle - best when a tile has few K blocks.
+//   BM = 256: tile 256 x 256 as two 128-row UMMAs that share the B stage, 3 stages of 64 KiB, one accumulator
+//             pair filling TMEM; 64 operand bytes per tensor cycle and 1.5 x the latency cover - best for long K.
+template <int BM>
+struct Cfg {
+  static constexpr int kHalves = BM / 128;
+  static constexpr int kStages = BM == 128 ? 4 : 3;
+  static constexpr int kAccBufs = BM == 128 ? 2 : 1;
+  static constexpr uint32_t kABytes = BM * UG_BK * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kRingBytes = kStages * kStageBytes;
+  static constexpr uint32_t kSmemBytes = kRingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiBytes;
+};
 
 struct Shared {
   uint64_t full[UG_STAGES];
@@ -240,6 +255,78 @@ __device__ __forceinline__ void store_row_bf16(__nv_bfloat16* p, const uint32_t 
   }
 }
 
+// Coalesced variant for full, 16-byte aligned chunks: the warp's 32 x 32 block goes through a
+// shared-memory buffer so that each store / reduction instruction covers whole 128-byte row
+// segments (4 rows of fp32, 8 rows of bf16) instead of 32 different rows.  This matters most for
+// red.add into a peer's memory, where every instruction becomes a few full NVLink packets.
+__device__ __forceinline__ void store_chunk_f32(float* sb, const uint32_t (&v)[32], int lane, float* c_base,
+                                                int64_t ldc, int rows_valid, int mode) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<uint4*>(sb + lane * kEpiRowFloats + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  __syncwarp();
+  const int rsub = lane >> 3, cseg = (lane & 7) * 4;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + rsub;
+    if (r < rows_valid) {
+      float4 x = *reinterpret_cast<const float4*>(sb + r * kEpiRowFloats + cseg);
+      float4* g = reinterpret_cast<float4*>(c_base + r * ldc + cseg);
+      if (mode == 1) {
+        red_add_v4_f32(g, x.x, x.y, x.z, x.w);
+      } else {
+        if (mode == 0) {
+          const float4 old = *g;
+          x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+        }
+        *g = x;
+      }
+    }
+  }
+  __syncwarp();
+}
+
+__device__ __forceinline__ void store_chunk_bf16(float* sbf, const uint32_t (&v)[32], int lane,
+                                                 __nv_bfloat16* c_base, int64_t ldc, int rows_valid, int mode) {
+  // 64 payload bytes per row, rows 80 bytes apart.
+  unsigned char* sb = reinterpret_cast<unsigned char*>(sbf);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 q;
+    q.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+    q.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+    q.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+    q.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+    *reinterpret_cast<uint4*>(sb + lane * 80 + j * 16) = q;
+  }
+  __syncwarp();
+  const int rsub = lane >> 2, cseg = (lane & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = i * 8 + rsub;
+    if (r < rows_valid) {
+      uint4 x = *reinterpret_cast<const uint4*>(sb + r * 80 + (lane & 3) * 16);
+      uint4* g = reinterpret_cast<uint4*>(c_base + r * ldc + cseg);
+      if (mode == 1) {
+        red_add_v4_bf16x2(g, x.x, x.y, x.z, x.w);
+      } else {
+        if (mode == 0) {
+          const uint4 old = *g;
+          const __nv_bfloat162* o = reinterpret_cast<const __nv_bfloat162*>(&old);
+          __nv_bfloat162* n = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 a = __bfloat1622float2(n[e]), b = __bfloat1622float2(o[e]);
+            n[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+          }
+        }
+        *g = x;
+      }
+    }
+  }
+  __syncwarp();
+}
+
 // ---------------------------------------------------------------- fetch warps
 // Copy one piece with the 32 lanes of a warp.  mode 0: 16-byte vectors, eight in
 // flight per lane.  mode 1: the source is only 2-byte aligned; every 16-byte
@@ -289,7 +376,13 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
   }
 }
 
+template <int BM>
 __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgFusedParams P) {
+  using C = Cfg<BM>;
+  constexpr uint32_t kABytes = C::kABytes;
+  constexpr uint32_t kStageBytes = C::kStageBytes;
+  constexpr uint32_t kRingBytes = C::kRingBytes;
+  constexpr uint32_t kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t ring = (raw_addr + 1023u) & ~1023u;            // 1024-byte aligned stage ring
@@ -309,7 +402,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
   ctl.deadline = global_timer_ns() + P.timeout_ns;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < UG_STAGES; ++s) {
+    for (int s = 0; s < C::kStages; ++s) {
       mbar_init(smem_u32(&sh->full[s]), 1);
       mbar_init(smem_u32(&sh->empty[s]), 1);
     }
@@ -364,7 +457,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
             if (sg.b_map < 256) seen[sg.b_map >> 6] |= 1ull << (sg.b_map & 63);
           }
           const int nkb = (sg.k_len + UG_BK - 1) / UG_BK;
-          const int ay = sg.a_row0 + tc.mt * UG_BM;
+          const int ay = sg.a_row0 + tc.mt * BM;
           const int bx = sg.b_col0 + tc.nt * UG_BN;
           for (int kb = 0; kb < nkb; ++kb) {
             ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, ctl);
@@ -376,7 +469,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
             tma_load_2d(sa, amap, sg.a_col0 + kb * UG_BK, ay, fb);
             for (int c = 0; c < n_chunks; ++c)
               tma_load_2d(sb + c * kBChunkBytes, bmap, bx + c * 64, sg.b_row0 + kb * UG_BK, fb);
-            if (++stage == UG_STAGES) { stage = 0; phase ^= 1u; }
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
         }
       }
@@ -394,7 +487,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
         ok = mbar_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1u, ctl);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * UG_BN;
+        const uint32_t d_tmem = tmem_base + (C::kAccBufs == 2 ? acc * UG_BN : 0u);
         for (int kb = 0; kb < t.kblocks; ++kb) {
           ok = mbar_wait(smem_u32(&sh->full[stage]), phase, ctl);
           if (!ok) break;
@@ -403,22 +496,26 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
           const uint32_t sb = sa + kABytes;
 #pragma unroll
           for (int ks = 0; ks < UG_BK / 16; ++ks) {
-            const uint64_t ad = make_desc_a(sa + ks * 32);
             const uint64_t bd = make_desc_b(sb + ks * 2048);
-            umma_bf16(d_tmem, ad, bd, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+            for (int h = 0; h < C::kHalves; ++h) {
+              const uint64_t ad = make_desc_a(sa + h * (128 * UG_BK * 2) + ks * 32);
+              umma_bf16(d_tmem + h * UG_BN, ad, bd, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            }
           }
           umma_commit(smem_u32(&sh->empty[stage]));
-          if (++stage == UG_STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         umma_commit(smem_u32(&sh->acc_full[acc]));
-        acc ^= 1u;
+        if (C::kAccBufs == 2) acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
     }
   } else if (warp < kFetchWarp0) {
     // ------------------------------------------------------------ epilogue
     const int quad = warp & 3;   // TMEM lane quadrant this warp may read
+    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + quad * (kEpiWarpBytes / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x) {
@@ -427,28 +524,41 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
       if (!ok) break;
       tc_fence_after();
-      const int row = tc.mt * UG_BM + quad * 32 + lane;
       const int col0 = tc.nt * UG_BN;
       const int n_rem = min(UG_BN, t.n - col0);
-      const bool row_ok = row < t.m;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * UG_BN;
-      for (int c = 0; c < n_rem; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + c, v);
-        tmem_ld_wait();
-        if (row_ok) {
+#pragma unroll
+      for (int h = 0; h < C::kHalves; ++h) {
+        const int row = tc.mt * BM + h * 128 + quad * 32 + lane;
+        const bool row_ok = row < t.m;
+        if (tc.mt * BM + h * 128 >= t.m) break;       // whole half outside the region (warp-uniform)
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                               (C::kAccBufs == 2 ? acc * UG_BN : static_cast<uint32_t>(h) * UG_BN);
+        for (int c = 0; c < n_rem; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
           const int ncols = min(32, n_rem - c);
-          const int64_t off = static_cast<int64_t>(row) * t.ldc + col0 + c;
-          if (t.c_dtype == 0)
-            store_row_f32(reinterpret_cast<float*>(t.c_ptr) + off, v, ncols, t.c_mode, t.c_vec != 0);
-          else
-            store_row_bf16(reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off, v, ncols, t.c_mode,
-                           t.c_vec != 0);
+          const int row0 = tc.mt * BM + h * 128 + quad * 32;          // first row of this warp
+          if (t.c_vec != 0 && ncols == 32) {
+            const int rows_valid = min(32, t.m - row0);               // <= 0 when the warp is past the region
+            const int64_t off0 = static_cast<int64_t>(row0) * t.ldc + col0 + c;
+            if (t.c_dtype == 0)
+              store_chunk_f32(epi_buf, v, lane, reinterpret_cast<float*>(t.c_ptr) + off0, t.ldc, rows_valid, t.c_mode);
+            else
+              store_chunk_bf16(epi_buf, v, lane, reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off0, t.ldc, rows_valid,
+                               t.c_mode);
+          } else if (row_ok) {
+            const int64_t off = static_cast<int64_t>(row) * t.ldc + col0 + c;
+            if (t.c_dtype == 0)
+              store_row_f32(reinterpret_cast<float*>(t.c_ptr) + off, v, ncols, t.c_mode, false);
+            else
+              store_row_bf16(reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off, v, ncols, t.c_mode, false);
+          }
         }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->acc_empty[acc]));
-      acc ^= 1u;
+      if (C::kAccBufs == 2) acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
   } else {
@@ -486,20 +596,30 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
 
 }  // namespace
 
-extern "C" int ug_fused_gemm_smem_bytes(void) { return static_cast<int>(kSmemBytes); }
+extern "C" int ug_fused_gemm_smem_bytes(void) { return static_cast<int>(Cfg<256>::kSmemBytes); }
 
-extern "C" int ug_fused_gemm(const UgFusedParams* params, int grid, void* stream) {
+namespace {
+template <int BM>
+int launch_fused(const UgFusedParams* params, int grid, cudaStream_t stream, int dev) {
   static bool configured[64] = {};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return static_cast<int>(e);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    e = cudaFuncSetAttribute(ug_fused_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kSmemBytes));
+    cudaError_t e = cudaFuncSetAttribute(ug_fused_gemm_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(Cfg<BM>::kSmemBytes));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
-  if (grid <= 0) return static_cast<int>(cudaErrorInvalidValue);
-  ug_fused_gemm_kernel<<<grid, kNumThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(*params);
+  ug_fused_gemm_kernel<BM><<<grid, kNumThreads, Cfg<BM>::kSmemBytes, stream>>>(*params);
   return static_cast<int>(cudaGetLastError());
+}
+}  // namespace
+
+extern "C" int ug_fused_gemm(const UgFusedParams* params, int grid, void* stream) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (grid <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (params->tile_m == 256) return launch_fused<256>(params, grid, st, dev);
+  if (params->tile_m == 0 || params->tile_m == 128) return launch_fused<128>(params, grid, st, dev);
+  return static_cast<int>(cudaErrorInvalidValue);
 }

@@ -17,7 +17,7 @@ extern "C" {
 // ----------------------------------------------------------------------------
 // Tile configuration of the fused GEMM (one CTA, cta_group::1).
 // ----------------------------------------------------------------------------
-#define UG_BM 128          // output tile rows   (UMMA M)
+#define UG_BM 128          // rows of one UMMA (and of the small output tile); the large tile has 256 rows
 #define UG_BN 256          // output tile cols   (UMMA N, fp32 accumulator = 256 TMEM columns)
 #define UG_BK 64           // K elements per pipeline stage (64 bf16 = one 128-byte swizzle row)
 #define UG_STAGES 4        // smem ring depth (4 x 48 KiB)
@@ -80,7 +80,7 @@ typedef struct {
   uint64_t status;        // uint32 status word (first error wins)
   int32_t num_maps, num_tasks, num_pieces, num_flags;
   int32_t total_tiles;
-  int32_t reserved;
+  int32_t tile_m;         // rows per output tile: 128 (0 means 128) or 256
   uint64_t timeout_ns;    // limit of every in-kernel wait
 } UgFusedParams;
 

@@ -16,6 +16,7 @@ stationary_c_plan.py:358-523 and stationary_b_plan.py:340-564.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Sequence
 
@@ -23,9 +24,12 @@ import numpy as np
 import torch
 
 from . import native
-from .native import BM, BN, BK
+from .native import BN, BK
 
 _PIECE_BYTES = 32 * 1024
+_EFF_128 = 0.66          # measured tensor-pipe share of the 128-row main loop
+_EFF_256 = 0.85          # expected share of the 256-row main loop
+_EPILOGUE_256 = 6000.0   # cycles of un-hidden epilogue per 256 x 256 tile
 
 
 def _round_up(x: int, m: int) -> int:
@@ -119,13 +123,18 @@ class FusedProgram:
 
 class FusedProgramBuilder:
     def __init__(self, device: torch.device, *, num_sms: int | None = None, timeout_ns: int = 4_000_000_000,
-                 range_check: Callable[[int, int, str], None] | None = None):
+                 range_check: Callable[[int, int, str], None] | None = None, tile_m: int | None = None):
         self.device = torch.device(device)
         if num_sms is None:
             num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.num_sms = int(num_sms)
         self.timeout_ns = int(timeout_ns)
         self.range_check = range_check
+        if tile_m is None and os.environ.get("UGEMM_TILE_M"):
+            tile_m = int(os.environ["UGEMM_TILE_M"])
+        if tile_m not in (None, 128, 256):
+            raise ValueError("tile_m must be 128 or 256")
+        self.tile_m = tile_m
         self.tasks: list[TaskSpec] = []
 
     def add_task(self, task: TaskSpec) -> None:
@@ -137,9 +146,35 @@ class FusedProgramBuilder:
                                  f"C {task.m}x{task.n}")
         self.tasks.append(task)
 
+    # ------------------------------------------------------------------ tile shape
+    def choose_tile_m(self) -> int:
+        """Pick 128- or 256-row output tiles from a cycle model of the persistent grid.
+
+        256-row tiles need 2/3 of the operand bytes per tensor cycle and keep the tensor pipe busier in
+        the main loop, but their accumulators fill TMEM, so the epilogue (about ``_EPILOGUE_256`` cycles)
+        is not hidden behind the next tile; with few K blocks per tile the 128-row tile wins."""
+        if self.tile_m is not None:
+            return self.tile_m
+        best = None
+        for bm, eff, epi in ((128, _EFF_128, 0.0), (256, _EFF_256, _EPILOGUE_256)):
+            per_cta = [0.0] * self.num_sms
+            tile = 0
+            for t in self.tasks:
+                kblocks = sum((a.cols + BK - 1) // BK for a, _ in t.segments)
+                tiles = ((t.m + bm - 1) // bm) * ((t.n + BN - 1) // BN)
+                cost = kblocks * (bm // 128) * 512.0 / eff + epi
+                for _ in range(tiles):
+                    per_cta[tile % self.num_sms] += cost
+                    tile += 1
+            total = max(per_cta) if per_cta else 0.0
+            if best is None or total < best[0]:
+                best = (total, bm)
+        return best[1] if best else 128
+
     # ------------------------------------------------------------------ lowering
     def build(self, status_ptr: int) -> FusedProgram:
         dev = self.device
+        BM = self.choose_tile_m()
         map_keys: dict[tuple, int] = {}
         map_specs: list[tuple] = []
 
@@ -204,7 +239,8 @@ class FusedProgramBuilder:
                 kblocks += (a.cols + BK - 1) // BK
             c_elem = 4 if task.c_dtype == native.DT_F32 else 2
             c_vec = int(task.c_ptr % 16 == 0 and (task.ldc * c_elem) % 16 == 0)
-            group_m = m_tiles if m_tiles <= 16 else 16
+            band = 2048 // BM
+            group_m = m_tiles if m_tiles <= band else band
             task_rows.append(dict(c_ptr=task.c_ptr, ldc=task.ldc, m=task.m, n=task.n, seg_begin=seg_begin,
                                   seg_count=len(task.segments), tile_begin=tile_begin, m_tiles=m_tiles,
                                   n_tiles=n_tiles, kblocks=kblocks, c_mode=task.c_mode, c_dtype=task.c_dtype,
@@ -321,9 +357,10 @@ class FusedProgramBuilder:
         params.num_pieces = len(ordered)
         params.num_flags = num_flags
         params.total_tiles = total_tiles
+        params.tile_m = BM
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
-                     pieces=len(ordered), staged_bytes=staging_bytes,
+                     pieces=len(ordered), staged_bytes=staging_bytes, tile_m=BM,
                      remote_bytes=sum(st.src.rows * st.src.cols * st.src.elem_bytes for st in staged.values()
                                       if st.src.remote), grid=grid)
         return FusedProgram(device=dev, tables=tables, staging=staging, params=params, grid=grid,

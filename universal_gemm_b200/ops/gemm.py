@@ -24,13 +24,13 @@ def _slice_of(t: torch.Tensor, *, remote: bool = False) -> OperandSlice:
 
 def build_gemm_program(a_parts: Sequence[torch.Tensor], b_parts: Sequence[torch.Tensor], c: torch.Tensor,
                        *, mode: int = native.C_ADD, stage_a: bool = False, stage_b: bool = False,
-                       timeout_ns: int = 4_000_000_000) -> FusedProgram:
+                       timeout_ns: int = 4_000_000_000, tile_m: int | None = None) -> FusedProgram:
     """``C (+)= sum_i a_parts[i] @ b_parts[i]``; ``stage_*`` forces the in-kernel staged
     copy path for that operand (as if it lived in a peer's memory)."""
     if c.dim() != 2 or c.stride(1) != 1:
         raise ValueError("C must be 2-D with unit column stride")
     state = DeviceState.get(c.device)
-    builder = FusedProgramBuilder(c.device, num_sms=state.num_sms, timeout_ns=timeout_ns)
+    builder = FusedProgramBuilder(c.device, num_sms=state.num_sms, timeout_ns=timeout_ns, tile_m=tile_m)
     segs = [(_slice_of(a, remote=stage_a), _slice_of(b, remote=stage_b)) for a, b in zip(a_parts, b_parts)]
     builder.add_task(TaskSpec(c_ptr=c.data_ptr(), ldc=c.stride(0), m=c.shape[0], n=c.shape[1], c_mode=mode,
                               c_dtype=torch_dtype_code(c.dtype), segments=segs))
@@ -47,8 +47,9 @@ def run_program(prog: FusedProgram, device: torch.device) -> None:
     state.launches += 1
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, mode: int = native.C_ADD) -> torch.Tensor:
+def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, *, mode: int = native.C_ADD,
+         tile_m: int | None = None) -> torch.Tensor:
     """``C (+)= A @ B`` on one GPU with the tcgen05 kernel.  A: [M, K] bf16, B: [K, N] bf16."""
-    prog = build_gemm_program([a], [b], c, mode=mode)
+    prog = build_gemm_program([a], [b], c, mode=mode, tile_m=tile_m)
     run_program(prog, c.device)
     return c

@@ -78,7 +78,7 @@ class FusedParams(ctypes.Structure):
         ("maps", c_uint64), ("tasks", c_uint64), ("segs", c_uint64), ("pieces", c_uint64),
         ("flags", c_uint64), ("flag_need", c_uint64), ("piece_counter", c_uint64), ("status", c_uint64),
         ("num_maps", c_int32), ("num_tasks", c_int32), ("num_pieces", c_int32), ("num_flags", c_int32),
-        ("total_tiles", c_int32), ("reserved", c_int32),
+        ("total_tiles", c_int32), ("tile_m", c_int32),
         ("timeout_ns", c_uint64),
     ]
 
