@@ -460,6 +460,13 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
           const int ay = sg.a_row0 + tc.mt * BM;
           const int bx = sg.b_col0 + tc.nt * UG_BN;
           for (int kb = 0; kb < nkb; ++kb) {
+            // Pull the operands of a later K block into L2 now: all CTAs walk K in step, so the first
+            // toucher of a line would otherwise pay the DRAM latency inside the smem ring's short cover.
+            if (P.prefetch_kblocks > 0 && kb + P.prefetch_kblocks < nkb) {
+              const int pk = (kb + P.prefetch_kblocks) * UG_BK;
+              tma_prefetch_l2_2d(amap, sg.a_col0 + pk, ay);
+              for (int c = 0; c < n_chunks; ++c) tma_prefetch_l2_2d(bmap, bx + c * 64, sg.b_row0 + pk);
+            }
             ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, ctl);
             if (!ok) break;
             const uint32_t fb = smem_u32(&sh->full[stage]);

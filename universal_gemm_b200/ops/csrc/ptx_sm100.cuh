@@ -63,6 +63,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, uint64_t map_addr
       : "memory");
 }
 
+// Ask TMA to bring one box into L2 only (no shared-memory destination, no completion signal).
+__device__ __forceinline__ void tma_prefetch_l2_2d(uint64_t map_addr, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map_addr), "r"(x), "r"(y)
+               : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result),

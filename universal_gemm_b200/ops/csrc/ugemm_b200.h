@@ -82,6 +82,8 @@ typedef struct {
   int32_t total_tiles;
   int32_t tile_m;         // rows per output tile: 128 (0 means 128) or 256
   uint64_t timeout_ns;    // limit of every in-kernel wait
+  int32_t prefetch_kblocks;  // L2 prefetch distance of the TMA producer in K blocks (0 = off)
+  int32_t reserved;
 } UgFusedParams;
 
 // ----------------------------------------------------------------------------

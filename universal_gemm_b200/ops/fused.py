@@ -29,6 +29,7 @@ from .native import BN, BK
 _PIECE_BYTES = 32 * 1024
 _EFF_128 = 0.66          # measured tensor-pipe share of the 128-row main loop
 _EFF_256 = 0.85          # expected share of the 256-row main loop
+_PREFETCH_KBLOCKS = 0     # L2 prefetch distance of the TMA producer (K blocks)
 _EPILOGUE_256 = 6000.0   # cycles of un-hidden epilogue per 256 x 256 tile
 
 
@@ -358,6 +359,7 @@ class FusedProgramBuilder:
         params.num_flags = num_flags
         params.total_tiles = total_tiles
         params.tile_m = BM
+        params.prefetch_kblocks = int(os.environ.get("UGEMM_PREFETCH_KBLOCKS", _PREFETCH_KBLOCKS))
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
                      pieces=len(ordered), staged_bytes=staging_bytes, tile_m=BM,

@@ -80,6 +80,7 @@ class FusedParams(ctypes.Structure):
         ("num_maps", c_int32), ("num_tasks", c_int32), ("num_pieces", c_int32), ("num_flags", c_int32),
         ("total_tiles", c_int32), ("tile_m", c_int32),
         ("timeout_ns", c_uint64),
+        ("prefetch_kblocks", c_int32), ("reserved", c_int32),
     ]
 
 
@@ -87,7 +88,7 @@ def check_layouts() -> None:
     assert SEGMENT_DTYPE.itemsize == 64, SEGMENT_DTYPE.itemsize
     assert TASK_DTYPE.itemsize == 64, TASK_DTYPE.itemsize
     assert PIECE_DTYPE.itemsize == 48, PIECE_DTYPE.itemsize
-    assert ctypes.sizeof(FusedParams) == 96, ctypes.sizeof(FusedParams)
+    assert ctypes.sizeof(FusedParams) == 104, ctypes.sizeof(FusedParams)
 
 
 check_layouts()
