@@ -1,0 +1,128 @@
+#!/usr/bin/env python3
+"""Peer-to-peer micro-benchmark over NVLink: one-sided pull (``ug_pull_2d``), one-sided
+accumulate (``ug_accumulate_2d``) and the fetch path of the fused kernel in isolation.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        benchmark/p2p_microbench.py --mib 256
+
+Every rank r reads from / adds into rank (r + 1) % size at the same time, so each link carries
+traffic in both directions.  Device-timed with CUDA events, max over ranks; prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import universal_gemm_b200 as ug  # noqa: E402
+from universal_gemm_b200.ops.device import DeviceState  # noqa: E402
+from universal_gemm_b200.utils.benchmarking import max_over_ranks, sync_all  # noqa: E402
+
+
+def timed(world, fn, iters, warmup=2):
+    for _ in range(warmup):
+        fn()
+    sync_all(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    sync_all(world)
+    return max_over_ranks(e0.elapsed_time(e1) / iters, world.device)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mib", type=int, default=256, help="payload per transfer")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--cols", type=int, default=8192, help="row length in bf16 elements")
+    ap.add_argument("--probe", action="store_true", help="sweep CTAs / threads / loads in flight of a flat peer copy")
+    args = ap.parse_args()
+    world = ug.init()
+    dev, rank, size = world.device, world.rank, world.size
+    st = DeviceState.get(dev)
+    cols = args.cols
+    rows = args.mib * 2 ** 20 // (cols * 2)
+    nbytes = rows * cols * 2
+    peer = (rank + 1) % size
+    out = {"world": size, "payload_mib": nbytes / 2 ** 20}
+
+    src = ug.empty(world, (rows * size, cols), "row", torch.bfloat16)       # one [rows, cols] tile per rank
+    src.local.normal_()
+    dst = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev)
+    sync_all(world)
+    ms = timed(world, lambda: st.pull_2d(dst.data_ptr(), cols * 2, src.tile_ptr(peer), src.ld * 2, rows, cols * 2, 2),
+               args.iters)
+    out["pull_kernel_gbs"] = nbytes / ms / 1e6
+    ms = timed(world, lambda: st.pull_2d(dst.data_ptr(), cols * 2, src.tile_ptr(rank), src.ld * 2, rows, cols * 2, 2),
+               args.iters)
+    out["local_copy_kernel_gbs"] = nbytes / ms / 1e6
+
+    if args.probe:
+        import ctypes
+        from universal_gemm_b200.ops import native as nat
+
+        fn = nat.lib().ug_copy_probe
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                       ctypes.c_void_p]
+        table = {}
+        for grid, threads in ((148, 128), (148, 256), (148, 512), (148, 1024), (296, 1024), (1184, 256)):
+            for unroll in (1, 4, 8, 16):
+                code = fn(dst.data_ptr(), src.tile_ptr(peer), nbytes, grid, threads, unroll, ctypes.c_void_p(st.stream()))
+                if code != 0:                 # e.g. too many registers for 1024 threads
+                    torch.cuda.synchronize()
+                    table[f"g{grid}_t{threads}_u{unroll}"] = None
+                    continue
+                ms = timed(world, lambda: fn(dst.data_ptr(), src.tile_ptr(peer), nbytes, grid, threads, unroll,
+                                             ctypes.c_void_p(st.stream())), 5, 1)
+                table[f"g{grid}_t{threads}_u{unroll}"] = round(nbytes / ms / 1e6, 1)
+        out["probe_gbs"] = table
+
+    acc = ug.zeros(world, (rows * size // 2, cols), "row", torch.float32)   # fp32: same bytes as above
+    part = torch.ones(rows // 2, cols, dtype=torch.float32, device=dev)
+    sync_all(world)
+    ms = timed(world, lambda: st.accumulate_2d(acc.tile_ptr(peer), acc.ld, part.data_ptr(), cols, rows // 2, cols, 0),
+               args.iters)
+    out["accumulate_kernel_gbs"] = nbytes / ms / 1e6
+
+    # Fetch path of the fused kernel: a GEMM with 128 rows whose B operand is the peer's tile, so the
+    # run time is the time the fetch warps need to stage B.
+    k = rows
+    a = ug.empty(world, (128 * size, k), "row", torch.bfloat16)
+    a.local.normal_()
+    c = ug.zeros(world, (128 * size, cols * size), "block" if False else "row", torch.float32)
+    bmat = ug.empty(world, (k, cols * size), "column", torch.bfloat16)
+    bmat.local.normal_()
+    sync_all(world)
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.fused import FusedProgramBuilder, OperandSlice, TaskSpec
+
+    builder = FusedProgramBuilder(dev, num_sms=st.num_sms)
+    builder.add_task(TaskSpec(c_ptr=c.tile_ptr(rank), ldc=c.ld, m=128, n=cols, c_mode=native.C_STORE, c_dtype=0,
+                              segments=[(OperandSlice(a.tile_ptr(rank), a.ld, 0, 0, 128, k),
+                                         OperandSlice(bmat.tile_ptr(peer), bmat.ld, 0, 0, k, cols, remote=True))]))
+    prog = builder.build(st.status_ptr)
+
+    def fused():
+        prog.reset_flags(st.stream())
+        prog.launch(st.stream())
+
+    ms = timed(world, fused, args.iters)
+    st.check()
+    out["fused_fetch_gbs"] = k * cols * 2 / ms / 1e6
+    out["fused_fetch_ms"] = ms
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    world.close()
+    torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

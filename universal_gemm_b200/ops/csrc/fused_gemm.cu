@@ -337,24 +337,22 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
   const char* src = reinterpret_cast<const char*>(pc.src);
   char* dst = reinterpret_cast<char*>(pc.dst);
   if (pc.mode == 0) {
-    constexpr int U = 8;
-    for (int64_t base = 0; base < total; base += 32 * U) {
-      uint4 buf[U];
-      int64_t off_d[U];
+    // Lanes run along a row, U rows are in flight per lane.  All loads of a batch are issued before
+    // the first store (the compiler barrier keeps the two phases apart), so one warp keeps
+    // U x 512 bytes on the wire.
+    constexpr int U = 16;
+    for (int r0 = 0; r0 < pc.rows; r0 += U) {
+      for (int c = lane; c < vec_per_row; c += 32) {
+        uint4 buf[U];
+        const char* s0 = src + static_cast<int64_t>(r0) * pc.src_ld + (static_cast<int64_t>(c) << 4);
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        int64_t i = base + u * 32 + lane;
-        off_d[u] = -1;
-        if (i < total) {
-          int r = static_cast<int>(i / vec_per_row);
-          int c = static_cast<int>(i - static_cast<int64_t>(r) * vec_per_row);
-          buf[u] = ld_stream_v4(src + r * pc.src_ld + (static_cast<int64_t>(c) << 4));
-          off_d[u] = r * pc.dst_ld + (static_cast<int64_t>(c) << 4);
-        }
-      }
+        for (int u = 0; u < U; ++u)
+          if (r0 + u < pc.rows) buf[u] = ld_stream_v4(s0 + u * pc.src_ld);
+        asm volatile("" ::: "memory");
+        char* d0 = dst + static_cast<int64_t>(r0) * pc.dst_ld + (static_cast<int64_t>(c) << 4);
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (off_d[u] >= 0) *reinterpret_cast<uint4*>(dst + off_d[u]) = buf[u];
+        for (int u = 0; u < U; ++u)
+          if (r0 + u < pc.rows) *reinterpret_cast<uint4*>(d0 + u * pc.dst_ld) = buf[u];
       }
     }
   } else {

@@ -132,6 +132,11 @@ int ug_accumulate_2d(uint64_t dst, int64_t dst_ld_elems, uint64_t src, int64_t s
 int ug_convert_2d(uint64_t dst, int64_t dst_ld_elems, int32_t dst_dtype, uint64_t src,
                   int64_t src_ld_elems, int32_t src_dtype, int32_t rows, int32_t cols, void* stream);
 
+// Tuning probe: flat 16-byte-vector copy with `grid` CTAs of `threads` threads and `unroll` loads in
+// flight per thread (1, 2, 4, 8 or 16); src may be peer memory.
+int ug_copy_probe(uint64_t dst, uint64_t src, int64_t bytes, int32_t grid, int32_t threads, int32_t unroll,
+                  void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -20,6 +20,7 @@ fused executor.
 """
 from __future__ import annotations
 
+import time
 from typing import Any, Sequence
 
 import torch
@@ -153,22 +154,30 @@ def _run_tilewise(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: S
     """Region by region: fetch the needed slices, multiply with the library matmul, add into C.
     Operand slices (not whole tiles) are fetched."""
     me = c.rank
+    clock = time.perf_counter
     for region in P.group_ops(ops):
         acc = None
         for op in region.ops:
+            t0 = clock()
             a_view = R.get_tile(a, op.a_idx, region=op.a_slice)
             b_view = R.get_tile(b, op.b_idx, region=op.b_slice)
+            t1 = clock()
             prod = torch.matmul(a_view.to(_acc_dtype(a.dtype)), b_view.to(_acc_dtype(b.dtype)))
             acc = prod if acc is None else acc.add_(prod)
+            t2 = clock()
+            profile.add_comm_sync(t1 - t0)
+            profile.add_compute(t2 - t1)
             R.release_tile(a_view)
             R.release_tile(b_view)
         owner = _owner(c, region.c_idx)
-        if owner == me:
+        t0 = clock()
+        if owner == me and kind == "c":
             c_view = R.tile(c, region.c_idx)[region.c_slice.rows.as_slice(), region.c_slice.cols.as_slice()]
-            if kind == "c":
-                c_view.add_(acc.to(c.dtype))
-                continue
+            c_view.add_(acc.to(c.dtype))
+            profile.add_compute(clock() - t0)
+            continue
         R.accumulate_tile(c, region.c_idx, acc.to(c.dtype), slice_=region.c_slice)
+        profile.add_comm_issue(clock() - t0)
 
 
 # ----------------------------------------------------------------------------- entry points
