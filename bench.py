@@ -37,9 +37,10 @@ def parse_args(argv=None):
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--m", type=int, default=8192)
-    ap.add_argument("--n", type=int, default=49152)
-    ap.add_argument("--k", type=int, default=12288)
+    # --dim-* spellings pass through torchrun's own parser ("--m" is an ambiguous prefix there)
+    ap.add_argument("--m", "--dim-m", dest="m", type=int, default=8192)
+    ap.add_argument("--n", "--dim-n", dest="n", type=int, default=49152)
+    ap.add_argument("--k", "--dim-k", dest="k", type=int, default=12288)
     ap.add_argument("--a-partition", default="row")
     ap.add_argument("--b-partition", default="column")
     ap.add_argument("--c-partition", default="row")

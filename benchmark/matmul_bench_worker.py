@@ -67,13 +67,14 @@ def _dtensor_iteration(dt_a, dt_b):
     return out.to_local()
 
 
-def run_worker(args: argparse.Namespace) -> None:
-    world = ug.init(device=args.device)
+def bench_case(world, args: argparse.Namespace) -> BenchResult | None:
+    """Run one case on an existing world; returns the record on rank 0 (None elsewhere)."""
     dev = world.device
     rank, size = world.rank, world.size
     in_dtype, c_dtype = DTYPES[args.dtype], DTYPES[args.c_dtype]
     torch.manual_seed(args.seed)          # same full matrices on every rank; each keeps its shard
     m, n, k = args.m, args.n, args.k
+    mats = None
     try:
         full_a = torch.randn(m, k, device=dev, dtype=torch.float32).to(in_dtype)
         full_b = (torch.randn(k, n, device=dev, dtype=torch.float32) * args.b_scale).to(in_dtype)
@@ -96,7 +97,6 @@ def run_worker(args: argparse.Namespace) -> None:
 
             dt_a, dt_b = shard(full_a, pa), shard(full_b, pb)
             iteration = lambda: _dtensor_iteration(dt_a, dt_b)  # noqa: E731
-            mats = None
         else:
             a = ug.distribute_tensor(full_a, world, args.a_partition, args.replication_factor)
             b = ug.distribute_tensor(full_b, world, args.b_partition, args.replication_factor)
@@ -144,18 +144,34 @@ def run_worker(args: argparse.Namespace) -> None:
                 if world.is_cuda:
                     torch.cuda.synchronize()
                 err = float((got.double() - want).abs().max().item())
-        if rank == 0:
-            flops = float(2.0 * m * n * k)
-            tflops = [flops / d / 1e12 for d in durations]
-            result = BenchResult(
-                method=args.method, m=m, n=n, k=k, a_partition=args.a_partition, b_partition=args.b_partition,
-                c_partition=args.c_partition, replication_factor=args.replication_factor,
-                warmup_iters=args.warmup_iters, measure_iters=args.measure_iters, world_size=size,
-                median_seconds=statistics.median(durations), min_seconds=min(durations), max_seconds=max(durations),
-                median_tflops=statistics.median(tflops), max_tflops=max(tflops), flops=flops,
-                theoretical_tflops=args.theoretical_tflops, dtype=args.dtype, c_dtype=args.c_dtype, device=dev.type,
-                timing="cuda_events_max_over_ranks" if world.is_cuda else "host_clock_max_over_ranks",
-                executed_method=executed, max_abs_error=err)
+        if rank != 0:
+            return None
+        flops = float(2.0 * m * n * k)
+        tflops = [flops / d / 1e12 for d in durations]
+        return BenchResult(
+            method=args.method, m=m, n=n, k=k, a_partition=args.a_partition, b_partition=args.b_partition,
+            c_partition=args.c_partition, replication_factor=args.replication_factor,
+            warmup_iters=args.warmup_iters, measure_iters=args.measure_iters, world_size=size,
+            median_seconds=statistics.median(durations), min_seconds=min(durations), max_seconds=max(durations),
+            median_tflops=statistics.median(tflops), max_tflops=max(tflops), flops=flops,
+            theoretical_tflops=args.theoretical_tflops, dtype=args.dtype, c_dtype=args.c_dtype, device=dev.type,
+            timing="cuda_events_max_over_ranks" if world.is_cuda else "host_clock_max_over_ranks",
+            executed_method=executed, max_abs_error=err)
+    finally:
+        if mats is not None:
+            world.barrier()
+            for mat in mats:
+                mat.free()
+            from universal_gemm_b200.parallel.exec import clear_program_cache
+
+            clear_program_cache()
+
+
+def run_worker(args: argparse.Namespace) -> None:
+    world = ug.init(device=args.device)
+    try:
+        result = bench_case(world, args)
+        if result is not None:
             os.makedirs(os.path.dirname(os.path.abspath(args.result_file)), exist_ok=True)
             with open(args.result_file, "w", encoding="utf-8") as f:
                 json.dump(asdict(result), f, indent=2, sort_keys=True)

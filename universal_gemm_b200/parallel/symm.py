@@ -158,9 +158,13 @@ class CudaIpcWorld(World):
         tensors[self.rank] = local
 
         def closer(own=ptr.value, opened=tuple(opened)):
+            # Collective: every rank unmaps its peers' memory before any owner frees it (freeing exported
+            # memory that an importer still has open is undefined).
             with torch.cuda.device(self.device):
+                torch.cuda.synchronize(self.device)
                 for p in opened:
                     L.ug_ipc_close(p)
+                dist.barrier(group=self.group)
                 L.ug_free(own)
 
         buf = SymmBuffer(self, nbytes, ptrs, tensors, closer)
@@ -183,7 +187,7 @@ class CudaIpcWorld(World):
     def close(self) -> None:
         torch.cuda.synchronize(self.device)
         self.barrier()
-        for buf in self._buffers:
+        for buf in self._buffers:       # same order on every rank: free() is collective
             buf.free()
         self._buffers.clear()
         self.barrier()
