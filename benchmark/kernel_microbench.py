@@ -36,7 +36,7 @@ def main() -> None:
     ap.add_argument("--mode", choices=["store", "add", "atomic"], default="store")
     ap.add_argument("--c-dtype", choices=["fp32", "bf16"], default="fp32")
     ap.add_argument("--no-torch", action="store_true")
-    ap.add_argument("--tile-m", type=int, choices=[128, 256], default=None, help="rows per output tile (default: model)")
+    ap.add_argument("--tile-m", type=lambda v: v if v == "pair" else int(v), default=None, help="rows per output tile (default: model)")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     m, n, k = args.m, args.n, args.k

@@ -40,7 +40,7 @@ def test_native_library_is_loaded():
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (512, 1024, 512), (300, 520, 200), (375, 1000, 376),
                                    (64, 4099, 1024), (2048, 4096, 1024), (1, 8, 8)])
 @pytest.mark.parametrize("mode", ["store", "add", "atomic"])
-@pytest.mark.parametrize("tile_m", [128, 256])
+@pytest.mark.parametrize("tile_m", [128, 256, "pair"])
 def test_gemm_kernel_fp32_out(m, n, k, mode, tile_m):
     from universal_gemm_b200.ops import native
     from universal_gemm_b200.ops.gemm import gemm
@@ -74,7 +74,7 @@ def test_gemm_kernel_bf16_out(mode):
 
 
 @pytest.mark.parametrize("stage_a,stage_b", [(True, False), (False, True), (True, True)])
-@pytest.mark.parametrize("tile_m", [128, 256])
+@pytest.mark.parametrize("tile_m", [128, 256, "pair"])
 def test_gemm_kernel_segments_and_staging(stage_a, stage_b, tile_m):
     from universal_gemm_b200.ops import native
     from universal_gemm_b200.ops.gemm import build_gemm_program, run_program

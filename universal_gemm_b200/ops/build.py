@@ -24,8 +24,8 @@ _CSRC = _OPS_DIR / "csrc"
 _LIB_PATH = _OPS_DIR / "libugemm_b200.so"
 _STAMP_PATH = _OPS_DIR / "libugemm_b200.so.stamp"
 
-SOURCES = ("fused_gemm.cu", "tile_ops.cu", "barrier.cu", "runtime.cu", "no_alloc.cu")
-HEADERS = ("ugemm_b200.h", "ptx_sm100.cuh", "no_alloc.h")
+SOURCES = ("fused_gemm.cu", "fused_gemm_pair.cu", "tile_ops.cu", "barrier.cu", "runtime.cu", "no_alloc.cu")
+HEADERS = ("ugemm_b200.h", "ptx_sm100.cuh", "fused_common.cuh", "no_alloc.h")
 
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -28,24 +28,13 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
-#include "ptx_sm100.cuh"
-#include "ugemm_b200.h"
+#include "fused_common.cuh"
 
 using namespace ugptx;
+using namespace ugfused;
 
 namespace {
 
-constexpr int kNumThreads = 320;
-constexpr int kProducerWarp = 0;
-constexpr int kMmaWarp = 1;
-constexpr int kFetchWarp0 = 6;  // warps 2..5 are the epilogue, 6..9 fetch
-
-constexpr uint32_t kBChunkBytes = UG_BK * 64 * 2;      // 8 KiB: 64 k rows x 64 n elements
-constexpr uint32_t kBBytes = 4 * kBChunkBytes;         // 32 KiB
-constexpr uint32_t kEpiRowFloats = 36;                 // 32 columns + 4 of padding: conflict-free v4 rows
-constexpr uint32_t kEpiWarpBytes = 32 * kEpiRowFloats * 4;
-constexpr uint32_t kEpiBytes = 4 * kEpiWarpBytes;      // one transpose buffer per epilogue warp
-constexpr uint32_t kTmemCols = 512;                    // 128 lanes x 512 fp32 columns: all of TMEM
 
 // Two tile shapes share the kernel source:
 //   BM = 128: tile 128 x 256, 4 stages of 48 KiB, two accumulators (epilogue overlaps the next main loop);
@@ -71,308 +60,6 @@ struct Shared {
   uint32_t tmem_base;
   volatile uint32_t abort;
 };
-
-struct WaitCtl {
-  volatile uint32_t* abort;
-  uint32_t* status;
-  uint64_t deadline;
-};
-
-__device__ __forceinline__ void raise_error(const WaitCtl& ctl, uint32_t code) {
-  atomicCAS(ctl.status, 0u, code);
-  *ctl.abort = 1u;
-}
-
-// Bounded mbarrier wait.  Returns false after an abort or a timeout.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtl& ctl) {
-  uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xffu) == 0u) {
-      if (*ctl.abort) return false;
-      if (global_timer_ns() > ctl.deadline) {
-        raise_error(ctl, UG_ERR_TIMEOUT_MBAR);
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-// Bounded wait until counter >= need (a staged chunk has fully landed).
-__device__ __forceinline__ bool flag_wait(const uint32_t* counter, uint32_t need, const WaitCtl& ctl) {
-  uint32_t spins = 0;
-  while (ld_acquire_gpu(counter) < need) {
-    __nanosleep(64);
-    if ((++spins & 0x3fu) == 0u) {
-      if (*ctl.abort) return false;
-      if (global_timer_ns() > ctl.deadline) {
-        raise_error(ctl, UG_ERR_TIMEOUT_FLAG);
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-struct TileCoord {
-  int task;
-  int mt, nt;
-};
-
-__device__ __forceinline__ int find_task(const UgTask* __restrict__ tasks, int num_tasks, int tile) {
-  int lo = 0, hi = num_tasks - 1;
-  while (lo < hi) {
-    int mid = (lo + hi + 1) >> 1;
-    if (tasks[mid].tile_begin <= tile) lo = mid; else hi = mid - 1;
-  }
-  return lo;
-}
-
-// Banded raster: inside a band of group_m tile rows, m runs fastest so the A band
-// stays in L2 while the CTAs sweep across n.
-__device__ __forceinline__ TileCoord locate(const UgTask* __restrict__ tasks, int num_tasks, int tile) {
-  TileCoord tc;
-  tc.task = find_task(tasks, num_tasks, tile);
-  const UgTask& t = tasks[tc.task];
-  int idx = tile - t.tile_begin;
-  int gm = t.group_m > 0 ? t.group_m : t.m_tiles;
-  int band_tiles = gm * t.n_tiles;
-  int band = idx / band_tiles;
-  int first_m = band * gm;
-  int band_m = min(gm, t.m_tiles - first_m);
-  int rem = idx - band * band_tiles;
-  tc.mt = first_m + rem % band_m;
-  tc.nt = rem / band_m;
-  return tc;
-}
-
-// UMMA shared-memory descriptors (sm_100 format, version 1, 128-byte swizzle).
-// A tile: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart (SBO).
-__device__ __forceinline__ uint64_t make_desc_a(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr >> 4) & 0x3fffu);
-  d |= static_cast<uint64_t>(1u) << 16;                  // LBO (unused for swizzled K-major)
-  d |= static_cast<uint64_t>(1024u >> 4) << 32;          // SBO
-  d |= static_cast<uint64_t>(1u) << 46;                  // descriptor version
-  d |= static_cast<uint64_t>(2u) << 61;                  // SWIZZLE_128B
-  return d;
-}
-// B tile: N-major.  One k row = 64 n elements = 128 bytes; 8-k-row groups are 1024
-// bytes apart (SBO); the next 64 n elements start kBChunkBytes later (LBO).
-__device__ __forceinline__ uint64_t make_desc_b(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr >> 4) & 0x3fffu);
-  d |= static_cast<uint64_t>(kBChunkBytes >> 4) << 16;   // LBO
-  d |= static_cast<uint64_t>(1024u >> 4) << 32;          // SBO
-  d |= static_cast<uint64_t>(1u) << 46;
-  d |= static_cast<uint64_t>(2u) << 61;
-  return d;
-}
-// Instruction descriptor: D fp32, A/B bf16, A K-major, B MN-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((n >> 3) << 17) |
-         ((static_cast<uint32_t>(UG_BM) >> 4) << 24);
-}
-
-// ---------------------------------------------------------------- epilogue stores
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
-// Write 32 consecutive accumulator columns of one row.  `ncols` (1..32) of them are
-// inside the region.  `p` points at the first of them.
-__device__ __forceinline__ void store_row_f32(float* p, const uint32_t (&v)[32], int ncols, int mode,
-                                              bool vec) {
-  if (vec && ncols == 32) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float a = __uint_as_float(v[4 * j + 0]), b = __uint_as_float(v[4 * j + 1]);
-      float c = __uint_as_float(v[4 * j + 2]), d = __uint_as_float(v[4 * j + 3]);
-      float4* q = reinterpret_cast<float4*>(p + 4 * j);
-      if (mode == 1) {
-        red_add_v4_f32(q, a, b, c, d);
-      } else {
-        if (mode == 0) {
-          float4 old = *q;
-          a += old.x; b += old.y; c += old.z; d += old.w;
-        }
-        *q = make_float4(a, b, c, d);
-      }
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (j < ncols) {
-        float a = __uint_as_float(v[j]);
-        if (mode == 1) red_add_f32(p + j, a);
-        else if (mode == 0) p[j] += a;
-        else p[j] = a;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* p, const uint32_t (&v)[32], int ncols,
-                                               int mode, bool vec) {
-  if (vec && ncols == 32) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float f[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * j + e]);
-      uint4* q = reinterpret_cast<uint4*>(p + 8 * j);
-      if (mode == 1) {
-        red_add_v4_bf16x2(q, pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
-                          pack_bf16x2(f[6], f[7]));
-      } else {
-        if (mode == 0) {
-          uint4 old = *q;
-          const __nv_bfloat162* o = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float2 of = __bfloat1622float2(o[e]);
-            f[2 * e] += of.x;
-            f[2 * e + 1] += of.y;
-          }
-        }
-        uint4 out;
-        out.x = pack_bf16x2(f[0], f[1]); out.y = pack_bf16x2(f[2], f[3]);
-        out.z = pack_bf16x2(f[4], f[5]); out.w = pack_bf16x2(f[6], f[7]);
-        *q = out;
-      }
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (j < ncols) {
-        float a = __uint_as_float(v[j]);
-        if (mode == 1) atomicAdd(p + j, __float2bfloat16_rn(a));
-        else if (mode == 0) p[j] = __float2bfloat16_rn(__bfloat162float(p[j]) + a);
-        else p[j] = __float2bfloat16_rn(a);
-      }
-    }
-  }
-}
-
-// Coalesced variant for full, 16-byte aligned chunks: the warp's 32 x 32 block goes through a
-// shared-memory buffer so that each store / reduction instruction covers whole 128-byte row
-// segments (4 rows of fp32, 8 rows of bf16) instead of 32 different rows.  This matters most for
-// red.add into a peer's memory, where every instruction becomes a few full NVLink packets.
-__device__ __forceinline__ void store_chunk_f32(float* sb, const uint32_t (&v)[32], int lane, float* c_base,
-                                                int64_t ldc, int rows_valid, int mode) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-    *reinterpret_cast<uint4*>(sb + lane * kEpiRowFloats + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-  __syncwarp();
-  const int rsub = lane >> 3, cseg = (lane & 7) * 4;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int r = i * 4 + rsub;
-    if (r < rows_valid) {
-      float4 x = *reinterpret_cast<const float4*>(sb + r * kEpiRowFloats + cseg);
-      float4* g = reinterpret_cast<float4*>(c_base + r * ldc + cseg);
-      if (mode == 1) {
-        red_add_v4_f32(g, x.x, x.y, x.z, x.w);
-      } else {
-        if (mode == 0) {
-          const float4 old = *g;
-          x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
-        }
-        *g = x;
-      }
-    }
-  }
-  __syncwarp();
-}
-
-__device__ __forceinline__ void store_chunk_bf16(float* sbf, const uint32_t (&v)[32], int lane,
-                                                 __nv_bfloat16* c_base, int64_t ldc, int rows_valid, int mode) {
-  // 64 payload bytes per row, rows 80 bytes apart.
-  unsigned char* sb = reinterpret_cast<unsigned char*>(sbf);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint4 q;
-    q.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-    q.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-    q.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-    q.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-    *reinterpret_cast<uint4*>(sb + lane * 80 + j * 16) = q;
-  }
-  __syncwarp();
-  const int rsub = lane >> 2, cseg = (lane & 3) * 8;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = i * 8 + rsub;
-    if (r < rows_valid) {
-      uint4 x = *reinterpret_cast<const uint4*>(sb + r * 80 + (lane & 3) * 16);
-      uint4* g = reinterpret_cast<uint4*>(c_base + r * ldc + cseg);
-      if (mode == 1) {
-        red_add_v4_bf16x2(g, x.x, x.y, x.z, x.w);
-      } else {
-        if (mode == 0) {
-          const uint4 old = *g;
-          const __nv_bfloat162* o = reinterpret_cast<const __nv_bfloat162*>(&old);
-          __nv_bfloat162* n = reinterpret_cast<__nv_bfloat162*>(&x);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 a = __bfloat1622float2(n[e]), b = __bfloat1622float2(o[e]);
-            n[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
-          }
-        }
-        *g = x;
-      }
-    }
-  }
-  __syncwarp();
-}
-
-// ---------------------------------------------------------------- fetch warps
-// Copy one piece with the 32 lanes of a warp.  mode 0: 16-byte vectors, eight in
-// flight per lane.  mode 1: the source is only 2-byte aligned; every 16-byte
-// destination vector is gathered from eight 2-byte loads.
-__device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
-  const int vec_per_row = (pc.row_bytes + 15) >> 4;
-  const int64_t total = static_cast<int64_t>(pc.rows) * vec_per_row;
-  const char* src = reinterpret_cast<const char*>(pc.src);
-  char* dst = reinterpret_cast<char*>(pc.dst);
-  if (pc.mode == 0) {
-    // Lanes run along a row, U rows are in flight per lane.  All loads of a batch are issued before
-    // the first store (the compiler barrier keeps the two phases apart), so one warp keeps
-    // U x 512 bytes on the wire.
-    constexpr int U = 16;
-    for (int r0 = 0; r0 < pc.rows; r0 += U) {
-      for (int c = lane; c < vec_per_row; c += 32) {
-        uint4 buf[U];
-        const char* s0 = src + static_cast<int64_t>(r0) * pc.src_ld + (static_cast<int64_t>(c) << 4);
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (r0 + u < pc.rows) buf[u] = ld_stream_v4(s0 + u * pc.src_ld);
-        asm volatile("" ::: "memory");
-        char* d0 = dst + static_cast<int64_t>(r0) * pc.dst_ld + (static_cast<int64_t>(c) << 4);
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (r0 + u < pc.rows) *reinterpret_cast<uint4*>(d0 + u * pc.dst_ld) = buf[u];
-      }
-    }
-  } else {
-    for (int64_t i = lane; i < total; i += 32) {
-      int r = static_cast<int>(i / vec_per_row);
-      int c = static_cast<int>(i - static_cast<int64_t>(r) * vec_per_row);
-      const uint16_t* s = reinterpret_cast<const uint16_t*>(src + r * pc.src_ld + (static_cast<int64_t>(c) << 4));
-      int valid = min(8, (pc.row_bytes - (c << 4)) >> 1);
-      uint16_t e[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) e[k] = (k < valid) ? s[k] : static_cast<uint16_t>(0);
-      uint4 out;
-      out.x = e[0] | (static_cast<uint32_t>(e[1]) << 16);
-      out.y = e[2] | (static_cast<uint32_t>(e[3]) << 16);
-      out.z = e[4] | (static_cast<uint32_t>(e[5]) << 16);
-      out.w = e[6] | (static_cast<uint32_t>(e[7]) << 16);
-      *reinterpret_cast<uint4*>(dst + r * pc.dst_ld + (static_cast<int64_t>(c) << 4)) = out;
-    }
-  }
-}
 
 template <int BM>
 __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgFusedParams P) {

@@ -1,0 +1,306 @@
+// Fused stationary GEMM, CTA-pair variant (tcgen05 cta_group::2) for sm_100a.
+//
+// Same tables, roles and fetch / remote-accumulate protocol as fused_gemm.cu, but two CTAs of a
+// cluster (two SMs) compute one 256 x 256 output tile together:
+//   * each CTA loads 128 rows of A and 128 of the 256 B columns per K block (32 KiB per stage, 6 stages),
+//     so an SM needs 64 operand bytes per tensor cycle, like the one-CTA 256-row tile;
+//   * each CTA's TMEM holds its 128 rows x 256 columns, i.e. only half of TMEM, so the accumulators are
+//     double buffered and the epilogue (which may push over NVLink) hides behind the next main loop,
+//     like the one-CTA 128-row tile.
+// CTA rank 0 of the pair issues the UMMAs; TMA loads of both CTAs complete on rank 0's "full" barrier
+// (cp.async.bulk.tensor with .cta_group::2, never multicast); UMMA completion is committed to the
+// "empty" / "accumulator full" barriers of both CTAs with two plain commits.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "fused_common.cuh"
+
+using namespace ugptx;
+using namespace ugfused;
+
+namespace {
+
+constexpr int kPairStages = 6;
+constexpr uint32_t kPairABytes = 128 * UG_BK * 2;               // 16 KiB: this CTA's 128 rows of A
+constexpr uint32_t kPairBBytes = 2 * kBChunkBytes;              // 16 KiB: this CTA's 128 columns of B
+constexpr uint32_t kPairStageBytes = kPairABytes + kPairBBytes; // 32 KiB
+constexpr uint32_t kPairRingBytes = kPairStages * kPairStageBytes;
+constexpr uint32_t kPairSmemBytes = kPairRingBytes + 1024 + 256 + kEpiBytes;
+
+struct PairShared {
+  uint64_t full[kPairStages];     // used in rank 0: bytes of both CTAs' loads
+  uint64_t empty[kPairStages];    // per CTA: stage consumed by the pair UMMAs
+  uint64_t acc_full[2];           // per CTA: accumulator buffer complete
+  uint64_t acc_empty[2];          // used in rank 0: both CTAs' epilogues drained the buffer
+  uint32_t tmem_base;
+  volatile uint32_t abort;
+};
+
+// Instruction descriptor of the pair UMMA: M = 256 (128 per CTA), N = 256.
+__device__ __forceinline__ uint32_t make_idesc_pair() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(const UgFusedParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t ring = (raw_addr + 1023u) & ~1023u;
+  PairShared* sh = reinterpret_cast<PairShared*>(smem_raw + (ring - raw_addr) + kPairRingBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader of the pair
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const UgTask* __restrict__ tasks = reinterpret_cast<const UgTask*>(P.tasks);
+  const UgSegment* __restrict__ segs = reinterpret_cast<const UgSegment*>(P.segs);
+  const uint32_t* flags = reinterpret_cast<const uint32_t*>(P.flags);
+  const int32_t* __restrict__ flag_need = reinterpret_cast<const int32_t*>(P.flag_need);
+
+  WaitCtl ctl;
+  ctl.abort = &sh->abort;
+  ctl.status = reinterpret_cast<uint32_t*>(P.status);
+  ctl.deadline = global_timer_ns() + P.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(smem_u32(&sh->full[s]), 1);
+      mbar_init(smem_u32(&sh->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->acc_full[b]), 1);
+      mbar_init(smem_u32(&sh->acc_empty[b]), 256);
+    }
+    sh->abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc_pair(smem_u32(&sh->tmem_base), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();              // barriers of both CTAs are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint64_t seen[4] = {0, 0, 0, 0};
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs) {
+        const TileCoord tc = locate(tasks, P.num_tasks, tile);
+        const UgTask& t = tasks[tc.task];
+        for (int s = 0; ok && s < t.seg_count; ++s) {
+          const UgSegment& sg = segs[t.seg_begin + s];
+          if (sg.a_flag >= 0) {
+            const int f = sg.a_flag + tc.mt;
+            ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
+          }
+          if (ok && sg.b_flag >= 0) {
+            const int f = sg.b_flag + tc.nt;
+            ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
+          }
+          if (!ok) break;
+          if (sg.a_flag >= 0 || sg.b_flag >= 0) fence_proxy_async();
+          const uint64_t amap = P.maps + static_cast<uint64_t>(sg.a_map) * 128u;
+          const uint64_t bmap = P.maps + static_cast<uint64_t>(sg.b_map) * 128u;
+          if (sg.a_map >= 256 || !((seen[sg.a_map >> 6] >> (sg.a_map & 63)) & 1ull)) {
+            tensormap_acquire(amap);
+            if (sg.a_map < 256) seen[sg.a_map >> 6] |= 1ull << (sg.a_map & 63);
+          }
+          if (sg.b_map >= 256 || !((seen[sg.b_map >> 6] >> (sg.b_map & 63)) & 1ull)) {
+            tensormap_acquire(bmap);
+            if (sg.b_map < 256) seen[sg.b_map >> 6] |= 1ull << (sg.b_map & 63);
+          }
+          const int nkb = (sg.k_len + UG_BK - 1) / UG_BK;
+          const int ay = sg.a_row0 + tc.mt * 256 + static_cast<int>(rank) * 128;
+          const int bx = sg.b_col0 + tc.nt * UG_BN + static_cast<int>(rank) * 128;
+          for (int kb = 0; kb < nkb; ++kb) {
+            ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, ctl);
+            if (!ok) break;
+            const uint32_t full_local = smem_u32(&sh->full[stage]);
+            const uint32_t full_leader = mapa_shared(full_local, 0);
+            const uint32_t sa = ring + stage * kPairStageBytes;
+            const uint32_t sb = sa + kPairABytes;
+            if (rank == 0) mbar_arrive_expect_tx(full_local, 2 * kPairStageBytes);
+            tma_load_2d_pair(sa, amap, sg.a_col0 + kb * UG_BK, ay, full_leader);
+            tma_load_2d_pair(sb, bmap, bx, sg.b_row0 + kb * UG_BK, full_leader);
+            tma_load_2d_pair(sb + kBChunkBytes, bmap, bx + 64, sg.b_row0 + kb * UG_BK, full_leader);
+            if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------ UMMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      const uint32_t idesc = make_idesc_pair();
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs) {
+        const TileCoord tc = locate(tasks, P.num_tasks, tile);
+        const UgTask& t = tasks[tc.task];
+        ok = mbar_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1u, ctl);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * UG_BN;
+        for (int kb = 0; kb < t.kblocks; ++kb) {
+          ok = mbar_wait(smem_u32(&sh->full[stage]), phase, ctl);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = ring + stage * kPairStageBytes;
+          const uint32_t sb = sa + kPairABytes;
+#pragma unroll
+          for (int ks = 0; ks < UG_BK / 16; ++ks)
+            umma_bf16_pair(d_tmem, make_desc_a(sa + ks * 32), make_desc_b(sb + ks * 2048), idesc,
+                           (kb > 0 || ks > 0) ? 1u : 0u);
+          const uint32_t e = smem_u32(&sh->empty[stage]);
+          umma_commit_pair(mapa_shared(e, 0));
+          umma_commit_pair(mapa_shared(e, 1));
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        const uint32_t f = smem_u32(&sh->acc_full[acc]);
+        umma_commit_pair(mapa_shared(f, 0));
+        umma_commit_pair(mapa_shared(f, 1));
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp < kFetchWarp0) {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int quad = warp & 3;
+    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + quad * (kEpiWarpBytes / 4);
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs) {
+      const TileCoord tc = locate(tasks, P.num_tasks, tile);
+      const UgTask& t = tasks[tc.task];
+      ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
+      if (!ok) break;
+      tc_fence_after();
+      const int col0 = tc.nt * UG_BN;
+      const int n_rem = min(UG_BN, t.n - col0);
+      const int row0 = tc.mt * 256 + static_cast<int>(rank) * 128 + quad * 32;
+      const int row = row0 + lane;
+      const bool row_ok = row < t.m;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * UG_BN;
+      if (row0 < t.m) {
+        for (int c = 0; c < n_rem; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+          const int ncols = min(32, n_rem - c);
+          if (t.c_vec != 0 && ncols == 32) {
+            const int rows_valid = min(32, t.m - row0);
+            const int64_t off0 = static_cast<int64_t>(row0) * t.ldc + col0 + c;
+            if (t.c_dtype == 0)
+              store_chunk_f32(epi_buf, v, lane, reinterpret_cast<float*>(t.c_ptr) + off0, t.ldc, rows_valid, t.c_mode);
+            else
+              store_chunk_bf16(epi_buf, v, lane, reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off0, t.ldc, rows_valid,
+                               t.c_mode);
+          } else if (row_ok) {
+            const int64_t off = static_cast<int64_t>(row) * t.ldc + col0 + c;
+            if (t.c_dtype == 0)
+              store_row_f32(reinterpret_cast<float*>(t.c_ptr) + off, v, ncols, t.c_mode, false);
+            else
+              store_row_bf16(reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off, v, ncols, t.c_mode, false);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(mapa_shared(smem_u32(&sh->acc_empty[acc]), 0));
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  } else {
+    // ------------------------------------------------------------ fetch warps
+    const UgPiece* __restrict__ pieces = reinterpret_cast<const UgPiece*>(P.pieces);
+    uint32_t* counter = reinterpret_cast<uint32_t*>(P.piece_counter);
+    uint32_t* wflags = reinterpret_cast<uint32_t*>(P.flags);
+    while (P.num_pieces > 0) {
+      uint32_t p = 0;
+      if (lane == 0) p = atomicAdd(counter, 1u);
+      p = __shfl_sync(0xffffffffu, p, 0);
+      if (p >= static_cast<uint32_t>(P.num_pieces) || sh->abort) break;
+      const UgPiece pc = pieces[p];
+      copy_piece(pc, lane);
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence();
+        red_release_gpu_add(wflags + pc.flag, 1u);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  if (sh->abort) {
+    const uint64_t until = global_timer_ns() + 200000ull;
+    while (global_timer_ns() < until) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();              // neither CTA leaves while the other may still touch its shared memory
+  tc_fence_after();
+  if (warp == kMmaWarp) tmem_dealloc_pair(tmem_base, kTmemCols);
+}
+
+}  // namespace
+
+extern "C" int ug_fused_gemm_pair(const UgFusedParams* params, int grid, void* stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (grid <= 0 || (grid & 1)) return static_cast<int>(cudaErrorInvalidValue);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(ug_fused_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kPairSmemBytes));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, ug_fused_gemm_pair_kernel, *params);
+  return static_cast<int>(e);
+}
+
+// Largest number of CTA pairs that can be resident at once on the current device (0 on error).
+extern "C" int ug_fused_gemm_pair_max_pairs(void) {
+  cudaError_t e = cudaFuncSetAttribute(ug_fused_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kPairSmemBytes));
+  if (e != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2, 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  e = cudaOccupancyMaxActiveClusters(&n, ug_fused_gemm_pair_kernel, &cfg);
+  return e == cudaSuccess ? n : 0;
+}

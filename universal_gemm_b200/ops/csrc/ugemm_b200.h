@@ -83,7 +83,7 @@ typedef struct {
   int32_t tile_m;         // rows per output tile: 128 (0 means 128) or 256
   uint64_t timeout_ns;    // limit of every in-kernel wait
   int32_t prefetch_kblocks;  // L2 prefetch distance of the TMA producer in K blocks (0 = off)
-  int32_t reserved;
+  int32_t cta_pair;          // 1: tables were lowered for the CTA-pair kernel (ug_fused_gemm_pair)
 } UgFusedParams;
 
 // ----------------------------------------------------------------------------
@@ -109,6 +109,9 @@ const char* ug_last_error(void);
 // Fused stationary GEMM: persistent tcgen05/TMEM kernel with in-kernel staging
 // of remote / misaligned operand slices and local or remote C accumulation.
 int ug_fused_gemm(const UgFusedParams* params, int grid, void* stream);
+// CTA-pair variant (cta_group::2): a cluster of two CTAs per 256 x 256 tile; `grid` must be even.
+int ug_fused_gemm_pair(const UgFusedParams* params, int grid, void* stream);
+int ug_fused_gemm_pair_max_pairs(void);
 // Dynamic shared memory the fused kernel asks for (for occupancy checks).
 int ug_fused_gemm_smem_bytes(void);
 

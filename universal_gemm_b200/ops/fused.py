@@ -118,8 +118,8 @@ class FusedProgram:
                                                  ctypes.c_void_p(stream)), "ug_zero_2d(flags)")
 
     def launch(self, stream: int) -> None:
-        native.check(native.lib().ug_fused_gemm(ctypes.byref(self.params), self.grid, ctypes.c_void_p(stream)),
-                     "ug_fused_gemm")
+        fn = native.lib().ug_fused_gemm_pair if self.params.cta_pair else native.lib().ug_fused_gemm
+        native.check(fn(ctypes.byref(self.params), self.grid, ctypes.c_void_p(stream)), "ug_fused_gemm")
 
 
 class FusedProgramBuilder:
@@ -132,9 +132,10 @@ class FusedProgramBuilder:
         self.timeout_ns = int(timeout_ns)
         self.range_check = range_check
         if tile_m is None and os.environ.get("UGEMM_TILE_M"):
-            tile_m = int(os.environ["UGEMM_TILE_M"])
-        if tile_m not in (None, 128, 256):
-            raise ValueError("tile_m must be 128 or 256")
+            env = os.environ["UGEMM_TILE_M"]
+            tile_m = env if env == "pair" else int(env)
+        if tile_m not in (None, 128, 256, "pair"):
+            raise ValueError('tile_m must be 128, 256 or "pair"')
         self.tile_m = tile_m
         self.tasks: list[TaskSpec] = []
 
@@ -175,7 +176,10 @@ class FusedProgramBuilder:
     # ------------------------------------------------------------------ lowering
     def build(self, status_ptr: int) -> FusedProgram:
         dev = self.device
-        BM = self.choose_tile_m()
+        variant = self.choose_tile_m()
+        pair = variant == "pair"            # two CTAs share a 256 x 256 tile; each loads 128 rows of A
+        BM = 256 if pair else variant
+        a_box_rows = 128 if pair else BM
         map_keys: dict[tuple, int] = {}
         map_specs: list[tuple] = []
 
@@ -220,12 +224,12 @@ class FusedProgramBuilder:
             for a, b in task.segments:
                 row = dict(a_flag=-1, b_flag=-1, k_len=a.cols)
                 if a.tma_ok():
-                    row["a_map"] = add_map(a.base, False, a.col0 + a.cols, a.row0 + a.rows, a.ld * a.elem_bytes, (BK, BM))
+                    row["a_map"] = add_map(a.base, False, a.col0 + a.cols, a.row0 + a.rows, a.ld * a.elem_bytes, (BK, a_box_rows))
                     row["a_row0"], row["a_col0"] = a.row0, a.col0
                     sa = None
                 else:
                     sa = stage("a", a)
-                    sa.map_index = add_map(sa.offset, True, a.cols, a.rows, sa.ld * a.elem_bytes, (BK, BM))
+                    sa.map_index = add_map(sa.offset, True, a.cols, a.rows, sa.ld * a.elem_bytes, (BK, a_box_rows))
                     row["a_map"], row["a_row0"], row["a_col0"], row["a_flag"] = sa.map_index, 0, 0, sa.flag_base
                 if b.tma_ok():
                     row["b_map"] = add_map(b.base, False, b.col0 + b.cols, b.row0 + b.rows, b.ld * b.elem_bytes, (64, BK))
@@ -251,7 +255,13 @@ class FusedProgramBuilder:
         if len(map_specs) > 4096:
             raise ValueError(f"plan needs {len(map_specs)} tensor maps (limit 4096)")
 
-        grid = self.num_sms if (staged or total_tiles >= self.num_sms) else max(total_tiles, 1)
+        if pair:
+            sms = self.num_sms // 2 * 2
+            grid = sms if (staged or 2 * total_tiles >= sms) else max(2 * total_tiles, 2)
+            wave_tiles = grid // 2
+        else:
+            grid = self.num_sms if (staged or total_tiles >= self.num_sms) else max(total_tiles, 1)
+            wave_tiles = grid
 
         # Pass 2: pieces of the staged copies, ordered by first use.
         staging = None
@@ -292,8 +302,8 @@ class FusedProgramBuilder:
             # Tile order of the persistent grid: CTA b runs tiles b, b + grid, ...  All CTAs walk
             # their K segments in order, so within a wave chunks are needed segment by segment.
             coords = self._tile_coords(task_rows)
-            for wave_start in range(0, total_tiles, grid):
-                wave = coords[wave_start:wave_start + grid]
+            for wave_start in range(0, total_tiles, wave_tiles):
+                wave = coords[wave_start:wave_start + wave_tiles]
                 max_segs = max(task_rows[t]["seg_count"] for t, _, _ in wave)
                 for s in range(max_segs):
                     for t, mt, nt in wave:
@@ -359,10 +369,11 @@ class FusedProgramBuilder:
         params.num_flags = num_flags
         params.total_tiles = total_tiles
         params.tile_m = BM
+        params.cta_pair = 1 if pair else 0
         params.prefetch_kblocks = int(os.environ.get("UGEMM_PREFETCH_KBLOCKS", _PREFETCH_KBLOCKS))
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
-                     pieces=len(ordered), staged_bytes=staging_bytes, tile_m=BM,
+                     pieces=len(ordered), staged_bytes=staging_bytes, tile_m="pair" if pair else BM,
                      remote_bytes=sum(st.src.rows * st.src.cols * st.src.elem_bytes for st in staged.values()
                                       if st.src.remote), grid=grid)
         return FusedProgram(device=dev, tables=tables, staging=staging, params=params, grid=grid,

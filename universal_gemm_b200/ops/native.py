@@ -80,7 +80,7 @@ class FusedParams(ctypes.Structure):
         ("num_maps", c_int32), ("num_tasks", c_int32), ("num_pieces", c_int32), ("num_flags", c_int32),
         ("total_tiles", c_int32), ("tile_m", c_int32),
         ("timeout_ns", c_uint64),
-        ("prefetch_kblocks", c_int32), ("reserved", c_int32),
+        ("prefetch_kblocks", c_int32), ("cta_pair", c_int32),
     ]
 
 
@@ -113,6 +113,9 @@ def lib() -> ctypes.CDLL:
                                        c_uint32, c_int]
     L.ug_fused_gemm.argtypes = [POINTER(FusedParams), c_int, c_void_p]
     L.ug_fused_gemm_smem_bytes.restype = c_int
+    L.ug_fused_gemm_pair.argtypes = [POINTER(FusedParams), c_int, c_void_p]
+    L.ug_fused_gemm_pair.restype = c_int
+    L.ug_fused_gemm_pair_max_pairs.restype = c_int
     L.ug_signal_barrier.argtypes = [c_uint64, c_int, c_int, c_uint32, c_uint64, c_uint64, c_uint64, c_int,
                                     c_void_p]
     L.ug_zero_2d.argtypes = [c_uint64, c_int64, c_int32, c_int64, c_void_p]
