@@ -28,9 +28,11 @@ from .native import BN, BK
 
 _PIECE_BYTES = 32 * 1024
 _EFF_128 = 0.66          # measured tensor-pipe share of the 128-row main loop
-_EFF_256 = 0.85          # expected share of the 256-row main loop
+_EFF_256 = 0.83          # ... of the one-CTA 256-row main loop
+_EFF_PAIR = 0.80         # ... of the CTA-pair main loop
+_LINK_BYTES_PER_CYCLE = 300.0    # ~570 GB/s of red.add into a peer at ~1.9 GHz
+_HBM_BYTES_PER_CYCLE = 8000.0    # epilogue stores mostly land in L2
 _PREFETCH_KBLOCKS = 0     # L2 prefetch distance of the TMA producer (K blocks)
-_EPILOGUE_256 = 6000.0   # cycles of un-hidden epilogue per 256 x 256 tile
 
 
 def _round_up(x: int, m: int) -> int:
@@ -76,6 +78,7 @@ class TaskSpec:
     c_mode: int
     c_dtype: int
     segments: list[tuple[OperandSlice, OperandSlice]] = field(default_factory=list)
+    c_remote: bool = False      # C lives in a peer's memory (the epilogue pushes over NVLink)
 
 
 @dataclass
@@ -149,28 +152,37 @@ class FusedProgramBuilder:
         self.tasks.append(task)
 
     # ------------------------------------------------------------------ tile shape
-    def choose_tile_m(self) -> int:
-        """Pick 128- or 256-row output tiles from a cycle model of the persistent grid.
+    def choose_tile_m(self):
+        """Pick the tile variant (128, 256 or "pair") from a cycle model of the persistent grid.
 
-        256-row tiles need 2/3 of the operand bytes per tensor cycle and keep the tensor pipe busier in
-        the main loop, but their accumulators fill TMEM, so the epilogue (about ``_EPILOGUE_256`` cycles)
-        is not hidden behind the next tile; with few K blocks per tile the 128-row tile wins."""
+        Per tile: main loop = K blocks x 512 tensor cycles per 128 rows / measured tensor-pipe share of the
+        variant; epilogue = C bytes of the tile over HBM, or over this CTA's share of the NVLink when C is a
+        peer's memory.  The 128-row tile and the CTA-pair tile hide the epilogue behind the next main loop
+        (cost max(main, epilogue)); the one-CTA 256-row tile fills TMEM and pays main + epilogue."""
         if self.tile_m is not None:
             return self.tile_m
+        sms = self.num_sms
         best = None
-        for bm, eff, epi in ((128, _EFF_128, 0.0), (256, _EFF_256, _EPILOGUE_256)):
-            per_cta = [0.0] * self.num_sms
+        for variant, rows, eff, hidden, workers in ((128, 128, _EFF_128, True, sms), (256, 256, _EFF_256, False, sms),
+                                                    ("pair", 256, _EFF_PAIR, True, sms // 2)):
+            if workers < 1:
+                continue
+            per_worker = [0.0] * workers
             tile = 0
             for t in self.tasks:
                 kblocks = sum((a.cols + BK - 1) // BK for a, _ in t.segments)
-                tiles = ((t.m + bm - 1) // bm) * ((t.n + BN - 1) // BN)
-                cost = kblocks * (bm // 128) * 512.0 / eff + epi
+                tiles = ((t.m + rows - 1) // rows) * ((t.n + BN - 1) // BN)
+                sm_rows = 128 if variant == "pair" else rows           # rows one SM multiplies per tile
+                main = kblocks * (sm_rows // 128) * 512.0 / eff
+                c_bytes = sm_rows * BN * (4 if t.c_dtype == native.DT_F32 else 2) * (2 if t.c_mode == native.C_ADD else 1)
+                epi = 1500.0 + c_bytes / (_LINK_BYTES_PER_CYCLE / sms if t.c_remote else _HBM_BYTES_PER_CYCLE / sms)
+                cost = max(main, epi) if hidden else main + epi
                 for _ in range(tiles):
-                    per_cta[tile % self.num_sms] += cost
+                    per_worker[tile % workers] += cost
                     tile += 1
-            total = max(per_cta) if per_cta else 0.0
+            total = max(per_worker)
             if best is None or total < best[0]:
-                best = (total, bm)
+                best = (total, variant)
         return best[1] if best else 128
 
     # ------------------------------------------------------------------ lowering

@@ -91,7 +91,7 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
                               rows=op.b_slice.shape[0], cols=op.b_slice.shape[1], remote=bo != me)
             segs.append((sa, sb))
         builder.add_task(TaskSpec(c_ptr=c_ptr, ldc=c.ld, m=m, n=n, c_mode=mode, c_dtype=torch_dtype_code(c.dtype),
-                                  segments=segs))
+                                  segments=segs, c_remote=c_owner != me))
     return builder.build(state.status_ptr)
 
 
