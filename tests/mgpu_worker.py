@@ -53,6 +53,23 @@ def main() -> int:
         b = ug.distribute_tensor(full_b, world, triple[1], rep, dtype=in_dtype)
         c = ug.distribute_tensor(full_c, world, triple[2], rep, dtype=torch.float32)
         iters = 2
+        ug.matmul(a, b, c, method=method, beta=0)                # C = A @ B, whatever C held
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        world.barrier()
+        got0 = c.full_tensor(replica=0).double()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        want0 = full_a.to(in_dtype).double() @ full_b.to(in_dtype).double()
+        err0 = (got0 - want0).abs().max().item()
+        if err0 > 3e-3 * max(1.0, want0.abs().max().item()):
+            failures += 1
+            print(f"[rank {rank}] FAIL beta=0 {m}x{n}x{k} {triple} rep={rep} {method}: max err {err0:.3e}", flush=True)
+        world.barrier()
+        c.local.copy_(full_c[ug.tile_bounds(c.layout, c.coord).rows.as_slice(), ug.tile_bounds(c.layout, c.coord).cols.as_slice()])
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        world.barrier()
         for _ in range(iters):
             ug.matmul(a, b, c, method=method)
         if dev.type == "cuda":

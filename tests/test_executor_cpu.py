@@ -103,3 +103,15 @@ def test_profile_counters(capsys):
     assert "accounted: 50.0%, unaccounted: 50.0%" in out
     profile.reset_stats()
     assert profile.snapshot() == {"comm_issue": 0.0, "comm_sync": 0.0, "compute": 0.0, "total_runtime": 0.0}
+
+
+def test_beta_zero_cpu():
+    full_a, full_b, full_c = make_inputs(20, 24, 28, seed=8)
+    cluster = ug.EmulatedCluster(4, "cpu")
+    mats = build_cluster_matrices(cluster, full_a, full_b, full_c, ("row", "column", "row"), 1, torch.float32,
+                                  torch.float32)
+    for a, b, c in mats:
+        ug.matmul(a, b, c, method="stationary_c", beta=0)
+    torch.testing.assert_close(mats[0][2].full_tensor().double(), full_a.double() @ full_b.double(), rtol=1e-4, atol=1e-4)
+    with pytest.raises(ValueError):
+        ug.matmul(*mats[0], beta=2)

@@ -210,3 +210,18 @@ def test_bounded_wait_reports_timeout_instead_of_hanging():
     assert slots[1, 0].item() == 1                                    # our own signal was delivered
     st.check()                                                        # status cleared, context alive
     assert torch.ones(4, device=_dev()).sum().item() == 4
+
+
+@pytest.mark.parametrize("method,triple", [("stationary_c", ("row", "row", "row")), ("stationary_c", ("block", "column", "block")),
+                                           ("stationary_b", ("row", "column", "row")), ("stationary_b", ("block", "column", "row"))])
+def test_beta_zero_overwrites_without_zeroing(method, triple):
+    """beta=0 on single-writer plans stores C = A @ B whatever C held before (no zeroing pass)."""
+    m, n, k = 520, 390, 450
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=4, device=_dev())
+    cluster = ug.EmulatedCluster(4, _dev())
+    mats = build_cluster_matrices(cluster, full_a, full_b, full_c * 100, triple, 1, torch.bfloat16, torch.float32)
+    for a, b, c in mats:
+        ug.matmul(a, b, c, method=method, beta=0)
+    _status_ok()
+    want = full_a.bfloat16().double() @ full_b.bfloat16().double()
+    torch.testing.assert_close(mats[0][2].full_tensor().double(), want, rtol=2e-3, atol=2e-3)

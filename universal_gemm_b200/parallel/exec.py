@@ -45,8 +45,13 @@ def _owner(dm: DistMatrix, idx: tuple[int, int], replica: int | None = None) -> 
 
 
 def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequence[MultiplyOp], *,
-               fuse_replica_reduce: bool = True, range_check: bool = True):
-    """Lower an op list into a :class:`~universal_gemm_b200.ops.fused.FusedProgram`."""
+               fuse_replica_reduce: bool = True, range_check: bool = True, beta: int = 1):
+    """Lower an op list into a :class:`~universal_gemm_b200.ops.fused.FusedProgram`.
+
+    ``beta=1`` is ``C += A @ B``.  ``beta=0`` is ``C = A @ B``: when every element of C has a single
+    writer in the whole plan the epilogue stores (locally or into the peer) and C is neither read nor
+    zeroed; otherwise the program keeps adding atomically and reports that C must be zeroed first.
+    Returns ``(program, needs_zero)``."""
     from ..ops import native
     from ..ops.device import DeviceState, torch_dtype_code
     from ..ops.fused import FusedProgramBuilder, OperandSlice, TaskSpec
@@ -57,6 +62,10 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
     me = c.rank
     rep_c = T.replication_factor(c.layout)
     push_to_origin = fuse_replica_reduce and rep_c > 1
+    # One writer per C element: Stationary-C without replicated C (the owner computes the whole K range),
+    # Stationary-B whose B is not split along K (each B tile owner covers all of K for its rows / columns).
+    single_writer = (kind == "c" and rep_c == 1) or (kind == "b" and T.grid_shape(b.layout)[0] == 1)
+    needs_zero = beta == 0 and not single_writer
 
     buffers = (a.buffer, b.buffer, c.buffer)
 
@@ -80,6 +89,8 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
             mode = native.C_ADD
         else:
             mode = native.C_ATOMIC
+        if beta == 0 and single_writer:
+            mode = native.C_STORE
         segs = []
         for op in region.ops:
             ao, bo = _owner(a, op.a_idx), _owner(b, op.b_idx)
@@ -92,15 +103,16 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
             segs.append((sa, sb))
         builder.add_task(TaskSpec(c_ptr=c_ptr, ldc=c.ld, m=m, n=n, c_mode=mode, c_dtype=torch_dtype_code(c.dtype),
                                   segments=segs, c_remote=c_owner != me))
-    return builder.build(state.status_ptr)
+    return builder.build(state.status_ptr), needs_zero
 
 
-def _program(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequence[MultiplyOp], fuse: bool):
-    key = (kind, a.buffer.ptr(a.rank), b.buffer.ptr(b.rank), c.buffer.ptr(c.rank), c.rank, fuse)
+def _program(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequence[MultiplyOp], fuse: bool,
+             beta: int = 1):
+    key = (kind, a.buffer.ptr(a.rank), b.buffer.ptr(b.rank), c.buffer.ptr(c.rank), c.rank, fuse, beta)
     hit = _program_cache.get(key)
     if hit is not None and (hit[0] is ops or hit[0] == ops) and hit[1] == (a.layout, b.layout, c.layout):
         return hit[2]
-    prog = lower_plan(kind, a, b, c, ops, fuse_replica_reduce=fuse)
+    prog = lower_plan(kind, a, b, c, ops, fuse_replica_reduce=fuse, beta=beta)
     _program_cache[key] = (ops, (a.layout, b.layout, c.layout), prog)
     return prog
 
@@ -112,12 +124,15 @@ def _can_fuse(a: DistMatrix, b: DistMatrix, c: DistMatrix) -> bool:
 
 # ----------------------------------------------------------------------------- fused executor
 def _run_fused(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequence[MultiplyOp], *,
-               fuse_replica_reduce: bool = True, barriers: bool = True) -> None:
+               fuse_replica_reduce: bool = True, barriers: bool = True, beta: int = 1) -> None:
     from ..ops.device import DeviceState
 
     world = c.world
     state = DeviceState.get(c.device)
-    prog = _program(kind, a, b, c, ops, fuse_replica_reduce)
+    prog, needs_zero = _program(kind, a, b, c, ops, fuse_replica_reduce, beta)
+    if needs_zero:        # several ranks add into C: clear it before the entry barrier lets anyone push
+        pad = c.local_padded
+        state.zero_2d(pad.data_ptr(), c.ld * c.itemsize, pad.shape[0], c.ld * c.itemsize)
     prof = profile.enabled
     if prof:
         e0, e1, e2, e3 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
@@ -182,7 +197,9 @@ def _run_tilewise(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: S
 
 # ----------------------------------------------------------------------------- entry points
 def _execute(kind: str, a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp] | None, *, local_only: bool,
-             executor: str | None, fuse_replica_reduce: bool, barriers: bool) -> list[MultiplyOp]:
+             executor: str | None, fuse_replica_reduce: bool, barriers: bool, beta: int = 1) -> list[MultiplyOp]:
+    if beta not in (0, 1):
+        raise ValueError("beta must be 0 (C = A @ B) or 1 (C += A @ B)")
     a, b, c = resolve(a), resolve(b), resolve(c)
     world = c.world
     rep_c = T.replication_factor(c.layout)
@@ -196,13 +213,15 @@ def _execute(kind: str, a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp] | None
             raise RuntimeError("the fused executor needs a CUDA world and bfloat16 A / B")
         if rep_c > 1 and not fuse_replica_reduce and T.my_replica(c.layout, c.rank) != 0:
             c.local_padded.zero_()
-        _run_fused(kind, a, b, c, ops, fuse_replica_reduce=fuse_replica_reduce, barriers=barriers)
+        _run_fused(kind, a, b, c, ops, fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta)
         if rep_c > 1 and not fuse_replica_reduce:
             R.reduce_replicas(c)
             world.device_barrier()
         return list(ops)
     if executor != "tilewise":
         raise ValueError(f"unknown executor {executor!r}")
+    if beta == 0:
+        c.local_padded.zero_()
     if rep_c > 1 and T.my_replica(c.layout, c.rank) != 0:
         # Partial results are reduced into replica 0; stale values of other replicas must not be re-added.
         c.local_padded.zero_()
@@ -221,20 +240,20 @@ def _execute(kind: str, a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp] | None
 def execute_stationary_c(a: Any, b: Any, c: Any, *, local_only: bool = True, release_remote_tiles: bool = True,
                          use_async: bool | None = None, max_outstanding_prefetch: int = 1,
                          executor: str | None = None, fuse_replica_reduce: bool = True,
-                         barriers: bool = True) -> list[MultiplyOp]:
+                         barriers: bool = True, beta: int = 1) -> list[MultiplyOp]:
     """``C += A @ B`` with the owner of every C tile computing it.  Returns the op list."""
     return _execute("c", a, b, c, None, local_only=local_only, executor=executor,
-                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers)
+                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta)
 
 
 def execute_stationary_b(a: Any, b: Any, c: Any, *, local_only: bool = True, release_remote_tiles: bool = True,
                          use_async: bool | None = None, max_outstanding_prefetch: int = 1,
                          max_outstanding_accumulates: int = 4, num_compute_streams: int = 2,
                          executor: str | None = None, fuse_replica_reduce: bool = True,
-                         barriers: bool = True) -> list[MultiplyOp]:
+                         barriers: bool = True, beta: int = 1) -> list[MultiplyOp]:
     """``C += A @ B`` with the owner of every B tile multiplying it and pushing partial C tiles."""
     return _execute("b", a, b, c, None, local_only=local_only, executor=executor,
-                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers)
+                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta)
 
 
 def execute_stationary_c_ops(a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp], *, release_remote_tiles: bool = True,
