@@ -93,6 +93,33 @@ def main() -> int:
         world.barrier()
         for mat in (a, b, c):
             mat.free()
+    # torch.addmm(c, a, b, out=c) on DTensors through the dispatch hook
+    m, n, k = 96, 80, 72
+    g = torch.Generator().manual_seed(7)
+    full_a, full_b = torch.randn(m, k, generator=g).to(dev), (torch.randn(k, n, generator=g) / 8).to(dev)
+    a = ug.distribute_tensor(full_a, world, "row", dtype=in_dtype)
+    b = ug.distribute_tensor(full_b, world, "column", dtype=in_dtype)
+    c = ug.zeros(world, (m, n), "block" if size > 1 else "row", torch.float32)
+    ug.mm_handler.enable("auto")
+    try:
+        dc = c.to_dtensor()
+        out = torch.addmm(dc, a.to_dtensor(), b.to_dtensor(), out=dc)
+        assert out is dc
+    finally:
+        ug.mm_handler.disable()
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    world.barrier()
+    got = c.full_tensor().double()
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    want = full_a.to(in_dtype).double() @ full_b.to(in_dtype).double()
+    ncases += 1
+    if (got - want).abs().max().item() > 3e-3 * max(1.0, want.abs().max().item()):
+        failures += 1
+        print(f"[rank {rank}] FAIL addmm hook", flush=True)
+    world.barrier()
+
     t = torch.tensor([failures], device=dev, dtype=torch.int64)
     dist.all_reduce(t)
     if rank == 0:

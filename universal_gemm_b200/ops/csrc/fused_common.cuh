@@ -12,10 +12,10 @@ namespace ugfused {
 
 using namespace ugptx;
 
-constexpr int kNumThreads = 320;
+constexpr int kNumThreads = 448;      // 14 warps: producer, UMMA, 4 epilogue, 8 fetch
 constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
-constexpr int kFetchWarp0 = 6;  // warps 2..5 are the epilogue, 6..9 fetch
+constexpr int kFetchWarp0 = 6;  // warps 2..5 are the epilogue, 6..13 fetch
 
 constexpr uint32_t kBChunkBytes = UG_BK * 64 * 2;      // 8 KiB: 64 k rows x 64 n elements
 constexpr uint32_t kBBytes = 4 * kBChunkBytes;         // 32 KiB
