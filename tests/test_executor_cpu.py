@@ -115,3 +115,18 @@ def test_beta_zero_cpu():
     torch.testing.assert_close(mats[0][2].full_tensor().double(), full_a.double() @ full_b.double(), rtol=1e-4, atol=1e-4)
     with pytest.raises(ValueError):
         ug.matmul(*mats[0], beta=2)
+
+
+def test_put_tile_and_signal_cpu():
+    cluster = ug.EmulatedCluster(3, "cpu")
+    wins = [ug.zeros(w, (3, 8), "row", torch.float32) for w in cluster.worlds()]
+    pads = [ug.SignalPad(w, slots=2) for w in cluster.worlds()]
+    for r, (win, pad) in enumerate(zip(wins, pads)):
+        ug.put_tile(win, ((r + 1) % 3, 0), torch.full((1, 4), float(r + 1)), slice_=ug.Slice2D(ug.Slice1D(0, 1), ug.Slice1D(2, 6)))
+        pad.signal((r + 1) % 3, slot=1)
+    for r, (win, pad) in enumerate(zip(wins, pads)):
+        pad.wait(slot=1, value=1)
+        assert win.local[0].tolist() == [0, 0] + [float((r - 1) % 3 + 1)] * 4 + [0, 0]
+    pads[0].timeout_ns = int(0.05e9)
+    with pytest.raises(TimeoutError):
+        pads[0].wait(slot=0, value=1)

@@ -33,11 +33,13 @@ from .parallel.plan import (  # noqa: F401
     clear_stationary_c_plan_cache, format_op, format_plan, format_stationary_b_op, format_stationary_b_plan,
     group_ops, select_method,
 )
-from .parallel.symm import CudaIpcWorld, EmulatedCluster, ShmWorld, SingleWorld, SymmHeap, World  # noqa: F401
+from .parallel.symm import (  # noqa: F401
+    CudaIpcWorld, DistComm, EmulatedCluster, FileComm, ShmWorld, SingleWorld, SymmHeap, World,
+)
 from .parallel.matrix import DistMatrix, distribute_tensor, empty, resolve, zeros  # noqa: F401
 from .parallel.runtime import (  # noqa: F401
     accumulate_tile, clear_peer_tensor_cache, default_world, free_get_tile_scratch, get_tile, get_tile_async,
-    init_scratch, reduce_replicas, reduce_replicas_async, release_tile, set_default_world, tile,
+    init_scratch, put_tile, reduce_replicas, reduce_replicas_async, release_tile, set_default_world, tile, SignalPad,
 )
 from .parallel.exec import (  # noqa: F401
     execute_stationary_b, execute_stationary_b_ops, execute_stationary_b_ops_async, execute_stationary_c,

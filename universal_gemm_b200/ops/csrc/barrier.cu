@@ -49,7 +49,38 @@ __global__ void __launch_bounds__(kBarrierThreads) signal_barrier_kernel(
   __threadfence_system();
 }
 
+// Point-to-point signalling for put + signal protocols: the sender's stores (stream-ordered before this
+// kernel) become visible before the counter moves; the receiver's wait is bounded like the barrier's.
+__global__ void signal_add_kernel(uint32_t* counter, uint32_t value) {
+  __threadfence_system();
+  red_release_sys_add(counter, value);
+}
+
+__global__ void signal_wait_kernel(const uint32_t* counter, uint32_t expected, uint32_t* status, uint64_t timeout_ns) {
+  const uint64_t deadline = global_timer_ns() + timeout_ns;
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ld_acquire_sys(counter) - expected) < 0) {
+    __nanosleep(100);
+    if ((++spins & 0x3fu) == 0u && global_timer_ns() > deadline) {
+      atomicCAS(status, 0u, static_cast<uint32_t>(UG_ERR_TIMEOUT_PEER));
+      break;
+    }
+  }
+  __threadfence_system();
+}
+
 }  // namespace
+
+extern "C" int ug_signal_add(uint64_t counter, uint32_t value, void* stream) {
+  signal_add_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<uint32_t*>(counter), value);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int ug_signal_wait(uint64_t counter, uint32_t expected, uint64_t status, uint64_t timeout_ns, void* stream) {
+  signal_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const uint32_t*>(counter), expected,
+                                                                      reinterpret_cast<uint32_t*>(status), timeout_ns);
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int ug_signal_barrier(const uint64_t* peer_slots_dev, int world, int rank, uint32_t seq,
                                  uint64_t status, uint64_t timeout_ns, uint64_t clear_ptr, int num_clear,

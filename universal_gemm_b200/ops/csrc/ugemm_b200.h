@@ -122,6 +122,10 @@ int ug_fused_gemm_smem_bytes(void);
 int ug_signal_barrier(const uint64_t* peer_slots_dev, int world, int rank, uint32_t seq,
                       uint64_t status, uint64_t timeout_ns, uint64_t clear_ptr, int num_clear,
                       void* stream);
+// Point-to-point signals: add `value` to a uint32 counter (possibly in a peer's memory) after all earlier
+// work of the stream; wait (bounded) until a local counter has reached `expected`.
+int ug_signal_add(uint64_t counter, uint32_t value, void* stream);
+int ug_signal_wait(uint64_t counter, uint32_t expected, uint64_t status, uint64_t timeout_ns, void* stream);
 // Zero `rows` x `row_bytes` with row pitch `ld_bytes` (16-byte vectors when aligned).
 int ug_zero_2d(uint64_t dst, int64_t ld_bytes, int32_t rows, int64_t row_bytes, void* stream);
 // dst[r, c] = src[r, c] for a 2-D slice; src may be peer memory.  elem_bytes in {2, 4}.

@@ -119,12 +119,14 @@ def lib() -> ctypes.CDLL:
     L.ug_signal_barrier.argtypes = [c_uint64, c_int, c_int, c_uint32, c_uint64, c_uint64, c_uint64, c_int,
                                     c_void_p]
     L.ug_zero_2d.argtypes = [c_uint64, c_int64, c_int32, c_int64, c_void_p]
+    L.ug_signal_add.argtypes = [c_uint64, c_uint32, c_void_p]
+    L.ug_signal_wait.argtypes = [c_uint64, c_uint32, c_uint64, c_uint64, c_void_p]
     L.ug_pull_2d.argtypes = [c_uint64, c_int64, c_uint64, c_int64, c_int32, c_int64, c_int32, c_void_p]
     L.ug_accumulate_2d.argtypes = [c_uint64, c_int64, c_uint64, c_int64, c_int32, c_int32, c_int32, c_void_p]
     L.ug_convert_2d.argtypes = [c_uint64, c_int64, c_int32, c_uint64, c_int64, c_int32, c_int32, c_int32,
                                 c_void_p]
     for name in ("ug_malloc", "ug_free", "ug_ipc_get_handle", "ug_ipc_open", "ug_ipc_close",
-                 "ug_encode_tensor_map", "ug_fused_gemm", "ug_signal_barrier", "ug_zero_2d", "ug_pull_2d",
+                 "ug_encode_tensor_map", "ug_fused_gemm", "ug_signal_barrier", "ug_signal_add", "ug_signal_wait", "ug_zero_2d", "ug_pull_2d",
                  "ug_accumulate_2d", "ug_convert_2d"):
         getattr(L, name).restype = c_int
     _configured = True

@@ -177,7 +177,12 @@ def empty(world: World, shape: tuple[int, int], partition: str | Partitioning, d
 
 def zeros(world: World, shape: tuple[int, int], partition: str | Partitioning, dtype: torch.dtype = torch.float32,
           replication_factor: int = 1) -> DistMatrix:
-    return empty(world, shape, partition, dtype, replication_factor).zero_()
+    dm = empty(world, shape, partition, dtype, replication_factor).zero_()
+    # Collective set-up call: nobody may write into a peer's shard before that peer has cleared it.
+    if world.is_cuda:
+        torch.cuda.synchronize(world.device)
+    world.barrier()
+    return dm
 
 
 def distribute_tensor(full: torch.Tensor, world: World, partition: str | Partitioning, replication_factor: int = 1,
@@ -198,4 +203,7 @@ def distribute_tensor(full: torch.Tensor, world: World, partition: str | Partiti
         full = buf
     dm.local_padded.zero_()
     dm.fill_from_full(full)
+    if world.is_cuda:
+        torch.cuda.synchronize(world.device)
+    world.barrier()
     return dm

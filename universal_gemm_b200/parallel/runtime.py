@@ -281,3 +281,86 @@ def gather_full(dm: DistMatrix, replica: int = 0) -> torch.Tensor:
                 DeviceState.get(dm.device).pull_2d(dst.data_ptr(), out.stride(0) * dm.itemsize, dm.tile_ptr(owner),
                                                    dm.ld * dm.itemsize, r, c * dm.itemsize, dm.itemsize)
     return out
+
+
+# ----------------------------------------------------------------------------- put + signal
+def put_tile(dt: Any, coord: tuple[int, int], view: torch.Tensor, *, slice_: Slice2D | None = None,
+             replica: int | None = None) -> None:
+    """``dt.tile(coord)[slice_] = view``, one-sided (the counterpart of ``get_tile``; stream-ordered on the GPU)."""
+    dm = resolve(dt)
+    _check_coord(dm, coord)
+    rows, cols = T.tile_shape(dm.layout, coord)
+    if slice_ is None:
+        slice_ = Slice2D(Slice1D(0, rows), Slice1D(0, cols))
+    if slice_.rows.stop > rows or slice_.cols.stop > cols or tuple(view.shape) != slice_.shape:
+        raise ValueError(f"view {tuple(view.shape)} / slice {slice_} do not fit tile shape {(rows, cols)}")
+    if view.dtype != dm.dtype:
+        raise RuntimeError(f"put_tile dtype mismatch: view={view.dtype}, dt={dm.dtype}")
+    owner = T.tile_rank(dm.layout, coord, replica=replica, rank=dm.rank)
+    if not dm.world.is_cuda:
+        dm.peer_tile(owner)[slice_.rows.as_slice(), slice_.cols.as_slice()] = view
+        return
+    if view.stride(1) != 1:
+        view = view.contiguous()
+    from ..ops.device import DeviceState
+
+    dst = dm.tile_ptr(owner) + (slice_.rows.start * dm.ld + slice_.cols.start) * dm.itemsize
+    DeviceState.get(dm.device).pull_2d(dst, dm.ld * dm.itemsize, view.data_ptr(), view.stride(0) * dm.itemsize,
+                                       view.shape[0], view.shape[1] * dm.itemsize, dm.itemsize)
+
+
+class SignalPad:
+    """``slots`` uint32 counters per rank in symmetric memory for put + signal protocols
+    (the window ``signal`` / ``wait_signal`` pair of the reference's torchcomms experiments,
+    torchcomms/put_02.py:43-55).  ``signal(peer, slot)`` is ordered after everything queued before it on the
+    current stream; ``wait(slot, value)`` blocks the *stream*, not the host, and is bounded on the device."""
+
+    def __init__(self, world: World, slots: int = 64, timeout_s: float = 10.0):
+        self.world = world
+        self.slots = int(slots)
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.buffer = world.alloc(self.slots * 4)
+        self.buffer.local.zero_()
+        if world.is_cuda:
+            torch.cuda.synchronize(world.device)
+        world.barrier()
+
+    def _counters(self, rank: int) -> torch.Tensor:
+        return self.buffer.tensor(rank)[: self.slots * 4].view(torch.int32)
+
+    def signal(self, peer: int, slot: int, value: int = 1) -> None:
+        if not 0 <= slot < self.slots:
+            raise ValueError(f"slot {slot} out of range")
+        if not self.world.is_cuda:
+            with _owner_lock(self.world, peer):
+                self._counters(peer)[slot] += value
+            return
+        import ctypes
+
+        from ..ops import native
+        from ..ops.device import DeviceState
+
+        st = DeviceState.get(self.world.device)
+        native.check(native.lib().ug_signal_add(self.buffer.ptr(peer) + 4 * slot, value, ctypes.c_void_p(st.stream())),
+                     "ug_signal_add")
+        st.launches += 1
+
+    def wait(self, slot: int, value: int) -> None:
+        if not self.world.is_cuda:
+            import time
+
+            deadline = time.monotonic() + self.timeout_ns * 1e-9
+            while int(self._counters(self.world.rank)[slot]) < value:
+                if time.monotonic() > deadline:
+                    raise TimeoutError(f"signal slot {slot} did not reach {value}")
+                time.sleep(0.0005)
+            return
+        import ctypes
+
+        from ..ops import native
+        from ..ops.device import DeviceState
+
+        st = DeviceState.get(self.world.device)
+        native.check(native.lib().ug_signal_wait(self.buffer.ptr(self.world.rank) + 4 * slot, value, st.status_ptr,
+                                                 self.timeout_ns, ctypes.c_void_p(st.stream())), "ug_signal_wait")
+        st.launches += 1

@@ -91,6 +91,76 @@ class World:
         pass
 
 
+# ----------------------------------------------------------------------------- control-plane communicators
+class DistComm:
+    """Control plane over a ``torch.distributed`` process group (bootstrap, handle exchange, host barriers)."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+
+        self._dist = dist
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+
+    def all_gather(self, obj):
+        out: list = [None] * self.size
+        self._dist.all_gather_object(out, obj, group=self.group)
+        return out
+
+    def barrier(self) -> None:
+        self._dist.barrier(group=self.group)
+
+
+class FileComm:
+    """Control plane over a shared directory: no process group needed.
+
+    Every collective writes one small file per rank and polls for the others; a rank that never shows up
+    makes the others raise ``TimeoutError`` after ``timeout_s`` instead of hanging.  This is the bootstrap
+    the reference does with a unique-id file and a 30 s poll (nvshmem_init_only.py:16-44), extended to all
+    handle exchanges and host barriers."""
+
+    def __init__(self, directory: str, rank: int, size: int, timeout_s: float = 30.0, poll_s: float = 0.005):
+        self.dir = directory
+        self.rank = int(rank)
+        self.size = int(size)
+        self.timeout_s = float(timeout_s)
+        self.poll_s = poll_s
+        self.group = None
+        self._round = 0
+        os.makedirs(directory, exist_ok=True)
+
+    def all_gather(self, obj):
+        import pickle
+        import time
+
+        k = self._round
+        self._round += 1
+        mine = os.path.join(self.dir, f"r{k}_{self.rank}.pkl")
+        with open(mine + ".tmp", "wb") as f:
+            pickle.dump(obj, f)
+        os.replace(mine + ".tmp", mine)
+        deadline = time.monotonic() + self.timeout_s
+        out = []
+        for r in range(self.size):
+            path = os.path.join(self.dir, f"r{k}_{r}.pkl")
+            while not os.path.exists(path):
+                if time.monotonic() > deadline:
+                    raise TimeoutError(f"rank {r} did not reach collective #{k} within {self.timeout_s:.1f} s")
+                time.sleep(self.poll_s)
+            with open(path, "rb") as f:
+                out.append(pickle.load(f))
+        if k >= 2:      # everyone has passed round k-2 once they wrote round k-1... keep the directory small
+            try:
+                os.unlink(os.path.join(self.dir, f"r{k - 2}_{self.rank}.pkl"))
+            except OSError:
+                pass
+        return out
+
+    def barrier(self) -> None:
+        self.all_gather(None)
+
+
 # ----------------------------------------------------------------------------- CUDA IPC
 class _CudaWrapper:
     """Exposes a raw device allocation through ``__cuda_array_interface__``."""
@@ -104,15 +174,14 @@ class _CudaWrapper:
 class CudaIpcWorld(World):
     """One process per GPU of one node; symmetric allocations over CUDA IPC."""
 
-    def __init__(self, group=None, device: torch.device | None = None, timeout_s: float = 10.0):
-        import torch.distributed as dist
+    def __init__(self, group=None, device: torch.device | None = None, timeout_s: float = 10.0, comm=None):
         from ..ops import native
         from ..ops.device import DeviceState
 
-        self._dist = dist
-        self.group = group
-        self.rank = dist.get_rank(group)
-        self.size = dist.get_world_size(group)
+        self.comm = comm if comm is not None else DistComm(group)
+        self.group = self.comm.group
+        self.rank = self.comm.rank
+        self.size = self.comm.size
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device())
         self.device = torch.device(device)
@@ -130,7 +199,7 @@ class CudaIpcWorld(World):
         self.barrier()
 
     def alloc(self, nbytes: int) -> SymmBuffer:
-        native, dist = self._native, self._dist
+        native = self._native
         L = native.lib()
         nbytes = _round_up(max(int(nbytes), 1), _ALIGN)
         with torch.cuda.device(self.device):
@@ -139,8 +208,7 @@ class CudaIpcWorld(World):
             handle = (ctypes.c_uint8 * 64)()
             native.check(L.ug_ipc_get_handle(ptr.value, ctypes.cast(handle, ctypes.c_void_p)), "ug_ipc_get_handle")
             mine = (bytes(handle), nbytes)
-            gathered: list = [None] * self.size
-            dist.all_gather_object(gathered, mine, group=self.group)
+            gathered = self.comm.all_gather(mine)
             ptrs, opened = [], []
             for r, (h, nb) in enumerate(gathered):
                 if nb != nbytes:
@@ -164,7 +232,7 @@ class CudaIpcWorld(World):
                 torch.cuda.synchronize(self.device)
                 for p in opened:
                     L.ug_ipc_close(p)
-                dist.barrier(group=self.group)
+                self.comm.barrier()
                 L.ug_free(own)
 
         buf = SymmBuffer(self, nbytes, ptrs, tensors, closer)
@@ -172,7 +240,7 @@ class CudaIpcWorld(World):
         return buf
 
     def barrier(self) -> None:
-        self._dist.barrier(group=self.group)
+        self.comm.barrier()
 
     def device_barrier(self, clear_ptr: int = 0, num_clear: int = 0) -> int:
         self._seq += 1
@@ -197,18 +265,14 @@ class CudaIpcWorld(World):
 class ShmWorld(World):
     """CPU ranks of one node; allocations are shared files under /dev/shm."""
 
-    def __init__(self, group=None, shm_dir: str = "/dev/shm"):
-        import torch.distributed as dist
-
-        self._dist = dist
-        self.group = group
-        self.rank = dist.get_rank(group)
-        self.size = dist.get_world_size(group)
+    def __init__(self, group=None, shm_dir: str = "/dev/shm", comm=None):
+        self.comm = comm if comm is not None else DistComm(group)
+        self.group = self.comm.group
+        self.rank = self.comm.rank
+        self.size = self.comm.size
         self.device = torch.device("cpu")
         self._dir = shm_dir
-        token = [uuid.uuid4().hex[:12] if self.rank == 0 else None]
-        dist.broadcast_object_list(token, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
-        self._token = token[0]
+        self._token = self.comm.all_gather(uuid.uuid4().hex[:12])[0]
         self._count = 0
         self._paths: list[str] = []
 
@@ -223,14 +287,14 @@ class ShmWorld(World):
         with open(mine, "wb") as f:
             f.truncate(nbytes)
         self._paths.append(mine)
-        self._dist.barrier(group=self.group)
+        self.comm.barrier()
         tensors = [torch.from_file(self._path(index, r), shared=True, size=nbytes, dtype=torch.uint8)
                    for r in range(self.size)]
-        self._dist.barrier(group=self.group)
+        self.comm.barrier()
         return SymmBuffer(self, nbytes, [t.data_ptr() for t in tensors], tensors, None)
 
     def barrier(self) -> None:
-        self._dist.barrier(group=self.group)
+        self.comm.barrier()
 
     def device_barrier(self, clear_ptr: int = 0, num_clear: int = 0) -> int:
         self.barrier()
