@@ -130,3 +130,25 @@ def test_put_tile_and_signal_cpu():
     pads[0].timeout_ns = int(0.05e9)
     with pytest.raises(TimeoutError):
         pads[0].wait(slot=0, value=1)
+
+
+def test_distributed_mlp_cpu():
+    from universal_gemm_b200.models import DistributedMLP
+
+    cluster = ug.EmulatedCluster(4, "cpu")
+    full_x = torch.randn(24, 16)
+    blocks = [DistributedMLP(w, 24, 16, 48, seed=3) for w in cluster.worlds()]
+    for blk in blocks:
+        blk.set_input(full_x)
+    for blk in blocks:        # phase 1 on every rank, then phase 2 (ranks of an emulated cluster run in turn)
+        ug.matmul(blk.x, blk.w1, blk.h, beta=0)
+    for blk in blocks:
+        blk.act.local.copy_(torch.nn.functional.gelu(blk.h.local))
+    for blk in blocks:        # K-split GEMM: several ranks add into y, so emulated ranks clear first, then add
+        blk.y.zero_()
+    for blk in blocks:
+        ug.matmul(blk.act, blk.w2, blk.y, beta=1)
+    torch.testing.assert_close(blocks[0].y.full_tensor(), blocks[0].reference(full_x), rtol=1e-4, atol=1e-4)
+    single = DistributedMLP(ug.SingleWorld("cpu"), 24, 16, 48, seed=3)
+    single.set_input(full_x)
+    torch.testing.assert_close(single.forward().full_tensor(), single.reference(full_x), rtol=1e-4, atol=1e-4)
