@@ -83,6 +83,8 @@ def main() -> None:
     ap.add_argument("--theoretical-tflops", type=float, default=None)
     ap.add_argument("--verify", action="store_true")
     ap.add_argument("--max-cases", type=int, default=0)
+    ap.add_argument("--only-methods", default="", help="comma-separated filter applied to the case list")
+    ap.add_argument("--max-m", type=int, default=0, help="skip shapes with more rows than this (0 = no limit)")
     ap.add_argument("--output-dir", default=str(THIS_DIR / "results" / f"sweep_{dt.datetime.now():%Y%m%d_%H%M%S}"))
     args = ap.parse_args()
 
@@ -99,6 +101,11 @@ def main() -> None:
                for rep in parse_int_list(args.replication_factors) if size % rep == 0
                for (a, b, c) in parse_partition_triples(args.partition_triples)]
         cases = [(s, mc) for s in shapes for mc in mcs]
+    if args.only_methods:
+        keep = set(parse_csv_list(args.only_methods))
+        cases = [(s, mc) for s, mc in cases if mc.method in keep]
+    if args.max_m > 0:
+        cases = [(s, mc) for s, mc in cases if s.m <= args.max_m]
     if args.max_cases > 0:
         cases = cases[: args.max_cases]
 
