@@ -225,3 +225,44 @@ def test_beta_zero_overwrites_without_zeroing(method, triple):
     _status_ok()
     want = full_a.bfloat16().double() @ full_b.bfloat16().double()
     torch.testing.assert_close(mats[0][2].full_tensor().double(), want, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("tile_m,m,n", [("pair", 512, 10240 - 17), (256, 512, 19712 - 5), (128, 256, 19712)])
+def test_gemm_kernel_tail_wave_uses_narrow_tiles(tile_m, m, n):
+    """Tile counts just above a multiple of the worker count: the trailing tile columns run as 128-wide tiles."""
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.gemm import build_gemm_program, run_program
+
+    torch.manual_seed(n)
+    k = 320
+    a = torch.randn(m, k, device=_dev()).bfloat16()
+    b = (torch.randn(k, n, device=_dev()) / k ** 0.5).bfloat16()
+    c = torch.full((m, n), 3.0, device=_dev())
+    prog = build_gemm_program([a], [b], c, mode=native.C_ADD, tile_m=tile_m)
+    assert prog.stats["tasks"] == 2                      # the task was split into a wide and a narrow part
+    run_program(prog, _dev())
+    _status_ok()
+    torch.testing.assert_close(c, a.float() @ b.float() + 3.0, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("method", ["stationary_b", "stationary_c"])
+def test_fused_tail_split_with_remote_tiles(method, monkeypatch):
+    """Two emulated ranks with 80 tiles each on 74 CTA pairs: the last three tile columns run as narrow tiles,
+    with the A slices staged from the 'peer' and (Stationary-B) the result stored into the peer's C."""
+    from universal_gemm_b200.parallel import exec as X
+
+    monkeypatch.setenv("UGEMM_TILE_M", "pair")
+    m, n, k = 1024, 10240, 256
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=6, device=_dev())
+    cluster = ug.EmulatedCluster(2, _dev())
+    mats = build_cluster_matrices(cluster, full_a, full_b, full_c, ("row", "column", "row"), 1, torch.bfloat16,
+                                  torch.float32)
+    X.clear_program_cache()
+    for a, b, c in mats:
+        ug.matmul(a, b, c, method=method, beta=0)
+    _status_ok()
+    stats = [v[2][0].stats for v in X._program_cache.values()]
+    assert all(s["tiles"] == 83 and s["tasks"] == 3 for s in stats), stats
+    want = full_a.bfloat16().double() @ full_b.bfloat16().double()
+    torch.testing.assert_close(mats[0][2].full_tensor().double(), want, rtol=2e-3, atol=2e-3)
+    X.clear_program_cache()

@@ -66,6 +66,14 @@ __device__ __forceinline__ bool flag_wait(const uint32_t* counter, uint32_t need
   return true;
 }
 
+// Columns per output tile of a task: UG_BN, or a narrower width stored in the upper half of c_vec
+// (used for the last, partly filled wave of tiles); bit 0 of c_vec says whether 16-byte accesses to C are legal.
+__device__ __forceinline__ int task_tile_n(const UgTask& t) {
+  const int v = t.c_vec >> 16;
+  return v > 0 ? v : UG_BN;
+}
+__device__ __forceinline__ bool task_c_vec(const UgTask& t) { return (t.c_vec & 1) != 0; }
+
 struct TileCoord {
   int task;
   int mt, nt;

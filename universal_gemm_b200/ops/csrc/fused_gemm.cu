@@ -116,7 +116,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
-        const int n_rem = t.n - tc.nt * UG_BN;
+        const int tile_n = task_tile_n(t);
+        const int n_rem = min(tile_n, t.n - tc.nt * tile_n);
         const int n_chunks = min(4, (n_rem + 63) >> 6);
         const uint32_t tx_bytes = kABytes + n_chunks * kBChunkBytes;
         for (int s = 0; ok && s < t.seg_count; ++s) {
@@ -126,7 +127,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
             ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
           }
           if (ok && sg.b_flag >= 0) {
-            const int f = sg.b_flag + tc.nt;
+            const int f = sg.b_flag + (tc.nt * tile_n) / UG_BN;
             ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
           }
           if (!ok) break;
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
           }
           const int nkb = (sg.k_len + UG_BK - 1) / UG_BK;
           const int ay = sg.a_row0 + tc.mt * BM;
-          const int bx = sg.b_col0 + tc.nt * UG_BN;
+          const int bx = sg.b_col0 + tc.nt * tile_n;
           for (int kb = 0; kb < nkb; ++kb) {
             // Pull the operands of a later K block into L2 now: all CTAs walk K in step, so the first
             // toucher of a line would otherwise pay the DRAM latency inside the smem ring's short cover.
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
-        const int n_rem = min(UG_BN, t.n - tc.nt * UG_BN);
+        const int n_rem = min(task_tile_n(t), t.n - tc.nt * task_tile_n(t));
         const uint32_t idesc = make_idesc(static_cast<uint32_t>((n_rem + 15) & ~15));
         ok = mbar_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1u, ctl);
         if (!ok) break;
@@ -216,8 +217,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
       if (!ok) break;
       tc_fence_after();
-      const int col0 = tc.nt * UG_BN;
-      const int n_rem = min(UG_BN, t.n - col0);
+      const int col0 = tc.nt * task_tile_n(t);
+      const int n_rem = min(task_tile_n(t), t.n - col0);
 #pragma unroll
       for (int h = 0; h < C::kHalves; ++h) {
         const int row = tc.mt * BM + h * 128 + quad * 32 + lane;
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
           tmem_ld_wait();
           const int ncols = min(32, n_rem - c);
           const int row0 = tc.mt * BM + h * 128 + quad * 32;          // first row of this warp
-          if (t.c_vec != 0 && ncols == 32) {
+          if (task_c_vec(t) && ncols == 32) {
             const int rows_valid = min(32, t.m - row0);               // <= 0 when the warp is past the region
             const int64_t off0 = static_cast<int64_t>(row0) * t.ldc + col0 + c;
             if (t.c_dtype == 0)

@@ -38,9 +38,9 @@ struct PairShared {
   volatile uint32_t abort;
 };
 
-// Instruction descriptor of the pair UMMA: M = 256 (128 per CTA), N = 256.
-__device__ __forceinline__ uint32_t make_idesc_pair() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+// Instruction descriptor of the pair UMMA: M = 256 (128 per CTA), N = n (256, or 128 for tail tiles).
+__device__ __forceinline__ uint32_t make_idesc_pair(uint32_t n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((n >> 3) << 17) | ((256u >> 4) << 24);
 }
 
 __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(const UgFusedParams P) {
@@ -96,6 +96,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
+        const int tile_n = task_tile_n(t);               // 256, or 128 for tail tiles: 128 / 64 columns per CTA
+        const int cta_cols = tile_n >> 1;
         for (int s = 0; ok && s < t.seg_count; ++s) {
           const UgSegment& sg = segs[t.seg_begin + s];
           if (sg.a_flag >= 0) {
@@ -103,7 +105,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
             ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
           }
           if (ok && sg.b_flag >= 0) {
-            const int f = sg.b_flag + tc.nt;
+            const int f = sg.b_flag + (tc.nt * tile_n) / UG_BN;
             ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
           }
           if (!ok) break;
@@ -120,7 +122,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
           }
           const int nkb = (sg.k_len + UG_BK - 1) / UG_BK;
           const int ay = sg.a_row0 + tc.mt * 256 + static_cast<int>(rank) * 128;
-          const int bx = sg.b_col0 + tc.nt * UG_BN + static_cast<int>(rank) * 128;
+          const int bx = sg.b_col0 + tc.nt * tile_n + static_cast<int>(rank) * cta_cols;
+          const uint32_t cta_bytes = kPairABytes + (cta_cols > 64 ? 2u : 1u) * kBChunkBytes;
           for (int kb = 0; kb < nkb; ++kb) {
             ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, ctl);
             if (!ok) break;
@@ -128,10 +131,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
             const uint32_t full_leader = mapa_shared(full_local, 0);
             const uint32_t sa = ring + stage * kPairStageBytes;
             const uint32_t sb = sa + kPairABytes;
-            if (rank == 0) mbar_arrive_expect_tx(full_local, 2 * kPairStageBytes);
+            if (rank == 0) mbar_arrive_expect_tx(full_local, 2 * cta_bytes);
             tma_load_2d_pair(sa, amap, sg.a_col0 + kb * UG_BK, ay, full_leader);
             tma_load_2d_pair(sb, bmap, bx, sg.b_row0 + kb * UG_BK, full_leader);
-            tma_load_2d_pair(sb + kBChunkBytes, bmap, bx + 64, sg.b_row0 + kb * UG_BK, full_leader);
+            if (cta_cols > 64) tma_load_2d_pair(sb + kBChunkBytes, bmap, bx + 64, sg.b_row0 + kb * UG_BK, full_leader);
             if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
           }
         }
@@ -141,11 +144,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     // ------------------------------------------------------------ UMMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-      const uint32_t idesc = make_idesc_pair();
       bool ok = true;
       for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
+        const uint32_t idesc = make_idesc_pair(static_cast<uint32_t>(task_tile_n(t)));
         ok = mbar_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1u, ctl);
         if (!ok) break;
         tc_fence_after();
@@ -185,8 +188,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
       if (!ok) break;
       tc_fence_after();
-      const int col0 = tc.nt * UG_BN;
-      const int n_rem = min(UG_BN, t.n - col0);
+      const int col0 = tc.nt * task_tile_n(t);
+      const int n_rem = min(task_tile_n(t), t.n - col0);
       const int row0 = tc.mt * 256 + static_cast<int>(rank) * 128 + quad * 32;
       const int row = row0 + lane;
       const bool row_ok = row < t.m;
@@ -197,7 +200,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
           tmem_ld_32x32(taddr + c, v);
           tmem_ld_wait();
           const int ncols = min(32, n_rem - c);
-          if (t.c_vec != 0 && ncols == 32) {
+          if (task_c_vec(t) && ncols == 32) {
             const int rows_valid = min(32, t.m - row0);
             const int64_t off0 = static_cast<int64_t>(row0) * t.ldc + col0 + c;
             if (t.c_dtype == 0)

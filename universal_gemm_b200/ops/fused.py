@@ -79,6 +79,7 @@ class TaskSpec:
     c_dtype: int
     segments: list[tuple[OperandSlice, OperandSlice]] = field(default_factory=list)
     c_remote: bool = False      # C lives in a peer's memory (the epilogue pushes over NVLink)
+    tile_n: int = BN            # columns per output tile (128 for tasks moved into the last, partial wave)
 
 
 @dataclass
@@ -192,6 +193,8 @@ class FusedProgramBuilder:
         pair = variant == "pair"            # two CTAs share a 256 x 256 tile; each loads 128 rows of A
         BM = 256 if pair else variant
         a_box_rows = 128 if pair else BM
+        workers = (self.num_sms // 2) if pair else self.num_sms
+        tasks = self._split_tail(self.tasks, BM, workers) if os.environ.get("UGEMM_TAIL_SPLIT", "1") != "0" else self.tasks
         map_keys: dict[tuple, int] = {}
         map_specs: list[tuple] = []
 
@@ -228,9 +231,9 @@ class FusedProgramBuilder:
         task_rows = []
         tile_begin = 0
         seg_sources: list[tuple[_Staged | None, _Staged | None]] = []
-        for task in self.tasks:
+        for task in tasks:
             m_tiles = (task.m + BM - 1) // BM
-            n_tiles = (task.n + BN - 1) // BN
+            n_tiles = (task.n + task.tile_n - 1) // task.tile_n
             seg_begin = len(seg_rows)
             kblocks = 0
             for a, b in task.segments:
@@ -256,12 +259,15 @@ class FusedProgramBuilder:
                 kblocks += (a.cols + BK - 1) // BK
             c_elem = 4 if task.c_dtype == native.DT_F32 else 2
             c_vec = int(task.c_ptr % 16 == 0 and (task.ldc * c_elem) % 16 == 0)
+            if task.tile_n != BN:
+                c_vec |= task.tile_n << 16
             band = 2048 // BM
             group_m = m_tiles if m_tiles <= band else band
             task_rows.append(dict(c_ptr=task.c_ptr, ldc=task.ldc, m=task.m, n=task.n, seg_begin=seg_begin,
                                   seg_count=len(task.segments), tile_begin=tile_begin, m_tiles=m_tiles,
                                   n_tiles=n_tiles, kblocks=kblocks, c_mode=task.c_mode, c_dtype=task.c_dtype,
                                   c_vec=c_vec, group_m=group_m))
+            task_rows[-1]["tile_n"] = task.tile_n
             tile_begin += m_tiles * n_tiles
         total_tiles = tile_begin
         if len(map_specs) > 4096:
@@ -323,7 +329,7 @@ class FusedProgramBuilder:
                         if s >= tr["seg_count"]:
                             continue
                         sa, sb = seg_sources[tr["seg_begin"] + s]
-                        for st, ci in ((sa, mt), (sb, nt)):
+                        for st, ci in ((sa, mt), (sb, nt * tr["tile_n"] // BN)):
                             if st is None:
                                 continue
                             key = (id(st), ci)
@@ -342,7 +348,8 @@ class FusedProgramBuilder:
         task_arr = np.zeros(max(len(task_rows), 1), dtype=native.TASK_DTYPE)
         for i, row in enumerate(task_rows):
             for k, v in row.items():
-                task_arr[i][k] = v
+                if k != "tile_n":
+                    task_arr[i][k] = v
         piece_arr = np.zeros(max(len(ordered), 1), dtype=native.PIECE_DTYPE)
         for i, row in enumerate(ordered):
             for k, v in row.items():
@@ -391,6 +398,49 @@ class FusedProgramBuilder:
         return FusedProgram(device=dev, tables=tables, staging=staging, params=params, grid=grid,
                             clear_ptr=params.flags if staged else 0, num_clear=(num_flags + 1) if staged else 0,
                             stats=stats)
+
+    @staticmethod
+    def _split_tail(tasks: list[TaskSpec], bm: int, workers: int) -> list[TaskSpec]:
+        """Halve the tile width of the tiles that would form the last, partly filled wave.
+
+        With T tiles on W workers the last wave holds T mod W tiles; if they are at most W / 2 and consist of whole
+        trailing tile columns of the last task(s), those columns become a task of their own with 128-column tiles:
+        twice as many tiles of half the cost, so the last wave costs half a tile time instead of a full one."""
+        counts = [((t.m + bm - 1) // bm) * ((t.n + BN - 1) // BN) for t in tasks]
+        total = sum(counts)
+        tail = total % workers if workers > 0 else 0
+        if total <= workers or tail == 0 or 2 * tail > workers:
+            return list(tasks)
+        out = list(tasks)
+        remaining = tail
+        idx = len(out) - 1
+        while remaining > 0 and idx >= 0:
+            t = out[idx]
+            m_tiles = (t.m + bm - 1) // bm
+            n_tiles = (t.n + BN - 1) // BN
+            if m_tiles > 2048 // bm:          # several raster bands: the last tiles are not whole columns
+                return list(tasks)
+            if m_tiles * n_tiles <= remaining:
+                out[idx] = FusedProgramBuilder._columns(t, 0, t.n, 128)
+                remaining -= m_tiles * n_tiles
+                idx -= 1
+                continue
+            if remaining % m_tiles:
+                return list(tasks)
+            cut = (n_tiles - remaining // m_tiles) * BN
+            out[idx:idx + 1] = [FusedProgramBuilder._columns(t, 0, cut, BN), FusedProgramBuilder._columns(t, cut, t.n, 128)]
+            remaining = 0
+        return out
+
+    @staticmethod
+    def _columns(t: TaskSpec, c0: int, c1: int, tile_n: int) -> TaskSpec:
+        """The sub-task of ``t`` that covers output columns ``[c0, c1)``."""
+        from dataclasses import replace
+
+        elem = 4 if t.c_dtype == native.DT_F32 else 2
+        segs = [(a, replace(b, col0=b.col0 + c0, cols=c1 - c0)) for a, b in t.segments]
+        return TaskSpec(c_ptr=t.c_ptr + c0 * elem, ldc=t.ldc, m=t.m, n=c1 - c0, c_mode=t.c_mode, c_dtype=t.c_dtype,
+                        segments=segs, c_remote=t.c_remote, tile_n=tile_n)
 
     @staticmethod
     def _tile_coords(task_rows: Sequence[dict]) -> list[tuple[int, int, int]]:
