@@ -262,7 +262,7 @@ def test_fused_tail_split_with_remote_tiles(method, monkeypatch):
         ug.matmul(a, b, c, method=method, beta=0)
     _status_ok()
     stats = [v[2][0].stats for v in X._program_cache.values()]
-    assert all(s["tiles"] == 83 and s["tasks"] == 3 for s in stats), stats
+    assert all(s["tiles"] == 86 and s["tasks"] == 3 for s in stats), stats   # 74 wide + 12 narrow tiles
     want = full_a.bfloat16().double() @ full_b.bfloat16().double()
     torch.testing.assert_close(mats[0][2].full_tensor().double(), want, rtol=2e-3, atol=2e-3)
     X.clear_program_cache()
