@@ -287,6 +287,54 @@ __device__ __forceinline__ void store_chunk_bf16(float* sbf, const uint32_t (&v)
   __syncwarp();
 }
 
+// 64 bf16 columns at a time: rows of 128 payload bytes, so that every store / reduction instruction covers
+// four full 128-byte row segments (half-line segments made the NVLink pushes of bf16 partial tiles inefficient).
+__device__ __forceinline__ void store_chunk_bf16_64(float* sbf, const uint32_t (&v0)[32], const uint32_t (&v1)[32],
+                                                    int lane, __nv_bfloat16* c_base, int64_t ldc, int rows_valid,
+                                                    int mode) {
+  unsigned char* sb = reinterpret_cast<unsigned char*>(sbf);          // row pitch 144 bytes (36 words)
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 q;
+    q.x = pack_bf16x2(__uint_as_float(v0[8 * j + 0]), __uint_as_float(v0[8 * j + 1]));
+    q.y = pack_bf16x2(__uint_as_float(v0[8 * j + 2]), __uint_as_float(v0[8 * j + 3]));
+    q.z = pack_bf16x2(__uint_as_float(v0[8 * j + 4]), __uint_as_float(v0[8 * j + 5]));
+    q.w = pack_bf16x2(__uint_as_float(v0[8 * j + 6]), __uint_as_float(v0[8 * j + 7]));
+    *reinterpret_cast<uint4*>(sb + lane * 144 + j * 16) = q;
+    q.x = pack_bf16x2(__uint_as_float(v1[8 * j + 0]), __uint_as_float(v1[8 * j + 1]));
+    q.y = pack_bf16x2(__uint_as_float(v1[8 * j + 2]), __uint_as_float(v1[8 * j + 3]));
+    q.z = pack_bf16x2(__uint_as_float(v1[8 * j + 4]), __uint_as_float(v1[8 * j + 5]));
+    q.w = pack_bf16x2(__uint_as_float(v1[8 * j + 6]), __uint_as_float(v1[8 * j + 7]));
+    *reinterpret_cast<uint4*>(sb + lane * 144 + 64 + j * 16) = q;
+  }
+  __syncwarp();
+  const int rsub = lane >> 3, seg = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + rsub;
+    if (r < rows_valid) {
+      uint4 x = *reinterpret_cast<const uint4*>(sb + r * 144 + seg * 16);
+      uint4* g = reinterpret_cast<uint4*>(c_base + r * ldc + seg * 8);
+      if (mode == 1) {
+        red_add_v4_bf16x2(g, x.x, x.y, x.z, x.w);
+      } else {
+        if (mode == 0) {
+          const uint4 old = *g;
+          const __nv_bfloat162* o = reinterpret_cast<const __nv_bfloat162*>(&old);
+          __nv_bfloat162* n = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 a = __bfloat1622float2(n[e]), b = __bfloat1622float2(o[e]);
+            n[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+          }
+        }
+        *g = x;
+      }
+    }
+  }
+  __syncwarp();
+}
+
 // ---------------------------------------------------------------- fetch warps
 // Copy one piece with the 32 lanes of a warp.  mode 0: 16-byte vectors, eight in
 // flight per lane.  mode 1: the source is only 2-byte aligned; every 16-byte
