@@ -152,3 +152,23 @@ def test_distributed_mlp_cpu():
     single = DistributedMLP(ug.SingleWorld("cpu"), 24, 16, 48, seed=3)
     single.set_input(full_x)
     torch.testing.assert_close(single.forward().full_tensor(), single.reference(full_x), rtol=1e-4, atol=1e-4)
+
+
+def test_redistribute_and_ring_matmul_cpu():
+    full = torch.randn(37, 29)
+    cluster = ug.EmulatedCluster(4, "cpu")
+    srcs = [ug.distribute_tensor(full, w, "row") for w in cluster.worlds()]
+    for target, rep in (("column", 1), ("block", 1), ("row", 2)):
+        outs = [ug.redistribute(s, target, rep) for s in srcs]
+        torch.testing.assert_close(outs[0].full_tensor(), full)
+        assert ug.grid_shape(outs[0]) == ug.grid_shape(ug.get_partitioning(target, rep, 4).layout((37, 29)))
+    halves = [ug.redistribute(s, "block", dtype=torch.bfloat16) for s in srcs]
+    torch.testing.assert_close(halves[0].full_tensor().float(), full.bfloat16().float())
+    full_a, full_b, full_c = make_inputs(16, 12, 20, seed=1)
+    mats = build_cluster_matrices(cluster, full_a, full_b, full_c, ("row", "row", "row"), 1, torch.float32, torch.float32)
+    for a, b, c in mats:
+        ug.row_partitioned_matmul(a, b, c)
+    torch.testing.assert_close(mats[0][2].full_tensor().double(), oracle(full_a, full_b, full_c, torch.float32),
+                               rtol=1e-4, atol=1e-4)
+    with pytest.raises(ValueError):
+        ug.row_partitioned_matmul(halves[0], mats[0][1], mats[0][2])

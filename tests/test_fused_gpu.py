@@ -266,3 +266,14 @@ def test_fused_tail_split_with_remote_tiles(method, monkeypatch):
     want = full_a.bfloat16().double() @ full_b.bfloat16().double()
     torch.testing.assert_close(mats[0][2].full_tensor().double(), want, rtol=2e-3, atol=2e-3)
     X.clear_program_cache()
+
+
+def test_redistribute_on_gpu():
+    full = torch.randn(301, 203, device=_dev())
+    cluster = ug.EmulatedCluster(4, _dev())
+    srcs = [ug.distribute_tensor(full, w, "block") for w in cluster.worlds()]
+    outs = [ug.redistribute(s, "column") for s in srcs]
+    halves = [ug.redistribute(s, "row", dtype=torch.bfloat16) for s in srcs]
+    torch.cuda.synchronize()
+    assert torch.equal(outs[2].full_tensor(), full)
+    assert torch.equal(halves[1].full_tensor().float(), full.bfloat16().float())

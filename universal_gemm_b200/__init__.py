@@ -39,11 +39,11 @@ from .parallel.symm import (  # noqa: F401
 from .parallel.matrix import DistMatrix, distribute_tensor, empty, resolve, zeros  # noqa: F401
 from .parallel.runtime import (  # noqa: F401
     accumulate_tile, clear_peer_tensor_cache, default_world, free_get_tile_scratch, get_tile, get_tile_async,
-    init_scratch, put_tile, reduce_replicas, reduce_replicas_async, release_tile, set_default_world, tile, SignalPad,
+    init_scratch, put_tile, redistribute, reduce_replicas, reduce_replicas_async, release_tile, set_default_world, tile, SignalPad,
 )
 from .parallel.exec import (  # noqa: F401
     execute_stationary_b, execute_stationary_b_ops, execute_stationary_b_ops_async, execute_stationary_c,
-    execute_stationary_c_ops, execute_stationary_c_ops_async, matmul,
+    execute_stationary_c_ops, execute_stationary_c_ops_async, matmul, row_partitioned_matmul,
 )
 from .parallel import handler as mm_handler  # noqa: F401
 from .utils import profile  # noqa: F401

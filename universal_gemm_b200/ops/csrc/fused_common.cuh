@@ -335,6 +335,36 @@ __device__ __forceinline__ void store_chunk_bf16_64(float* sbf, const uint32_t (
   __syncwarp();
 }
 
+// Any alignment, any width: the 32 x 32 block goes through shared memory and every instruction handles 32
+// consecutive columns of ONE row (a coalesced, possibly misaligned 128-byte / 64-byte segment).  Used when C
+// rows are not 16-byte aligned (odd column offsets of odd-shaped partitions) and for ragged right edges.
+__device__ __forceinline__ void store_chunk_scalar(float* sb, const uint32_t (&v)[32], int lane, uint64_t c_ptr,
+                                                   int64_t elem_off, int64_t ldc, int rows_valid, int ncols, int mode,
+                                                   int dtype) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<uint4*>(sb + lane * kEpiRowFloats + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  __syncwarp();
+  if (lane < ncols) {
+    for (int r = 0; r < rows_valid; ++r) {
+      const float x = sb[r * kEpiRowFloats + lane];
+      const int64_t off = elem_off + r * ldc + lane;
+      if (dtype == 0) {
+        float* g = reinterpret_cast<float*>(c_ptr) + off;
+        if (mode == 1) red_add_f32(g, x);
+        else if (mode == 0) *g += x;
+        else *g = x;
+      } else {
+        __nv_bfloat16* g = reinterpret_cast<__nv_bfloat16*>(c_ptr) + off;
+        if (mode == 1) atomicAdd(g, __float2bfloat16_rn(x));
+        else if (mode == 0) *g = __float2bfloat16_rn(__bfloat162float(*g) + x);
+        else *g = __float2bfloat16_rn(x);
+      }
+    }
+  }
+  __syncwarp();
+}
+
 // ---------------------------------------------------------------- fetch warps
 // Copy one piece with the 32 lanes of a warp.  mode 0: 16-byte vectors, eight in
 // flight per lane.  mode 1: the source is only 2-byte aligned; every 16-byte

@@ -221,8 +221,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       const int n_rem = min(task_tile_n(t), t.n - col0);
 #pragma unroll
       for (int h = 0; h < C::kHalves; ++h) {
-        const int row = tc.mt * BM + h * 128 + quad * 32 + lane;
-        const bool row_ok = row < t.m;
         if (tc.mt * BM + h * 128 >= t.m) break;       // whole half outside the region (warp-uniform)
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                (C::kAccBufs == 2 ? acc * UG_BN : static_cast<uint32_t>(h) * UG_BN);
@@ -253,12 +251,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
             else
               store_chunk_bf16(epi_buf, v, lane, reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off0, t.ldc, rows_valid,
                                t.c_mode);
-          } else if (row_ok) {
-            const int64_t off = static_cast<int64_t>(row) * t.ldc + col0 + c;
-            if (t.c_dtype == 0)
-              store_row_f32(reinterpret_cast<float*>(t.c_ptr) + off, v, ncols, t.c_mode, false);
-            else
-              store_row_bf16(reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off, v, ncols, t.c_mode, false);
+          } else {
+            store_chunk_scalar(epi_buf, v, lane, t.c_ptr, static_cast<int64_t>(row0) * t.ldc + col0 + c, t.ldc,
+                               min(32, t.m - row0), ncols, t.c_mode, t.c_dtype);
           }
         }
       }

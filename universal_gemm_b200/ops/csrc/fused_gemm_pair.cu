@@ -191,8 +191,6 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       const int col0 = tc.nt * task_tile_n(t);
       const int n_rem = min(task_tile_n(t), t.n - col0);
       const int row0 = tc.mt * 256 + static_cast<int>(rank) * 128 + quad * 32;
-      const int row = row0 + lane;
-      const bool row_ok = row < t.m;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * UG_BN;
       if (row0 < t.m) {
         for (int c = 0; c < n_rem; c += 32) {
@@ -221,12 +219,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
             else
               store_chunk_bf16(epi_buf, v, lane, reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off0, t.ldc, rows_valid,
                                t.c_mode);
-          } else if (row_ok) {
-            const int64_t off = static_cast<int64_t>(row) * t.ldc + col0 + c;
-            if (t.c_dtype == 0)
-              store_row_f32(reinterpret_cast<float*>(t.c_ptr) + off, v, ncols, t.c_mode, false);
-            else
-              store_row_bf16(reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off, v, ncols, t.c_mode, false);
+          } else {
+            store_chunk_scalar(epi_buf, v, lane, t.c_ptr, static_cast<int64_t>(row0) * t.ldc + col0 + c, t.ldc,
+                               min(32, t.m - row0), ncols, t.c_mode, t.c_dtype);
           }
         }
       }

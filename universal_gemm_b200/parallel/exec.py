@@ -281,6 +281,18 @@ def execute_stationary_b_ops_async(a: Any, b: Any, c: Any, ops: Sequence[Multipl
     _execute("b", a, b, c, ops, local_only=True, executor=None, fuse_replica_reduce=True, barriers=barriers)
 
 
+def row_partitioned_matmul(a: Any, b: Any, c: Any, **kwargs) -> list[MultiplyOp]:
+    """``C += A @ B`` for three row-partitioned matrices as a ring: every rank walks the B row tiles starting at
+    its own index and multiplies them with the matching K slice of its local A rows.  This is the Stationary-C
+    plan of the row / row / row triple (the reference keeps a hand-written version of it,
+    dtensor_mm_handler.py:19-79); layouts are checked, execution is the fused kernel."""
+    la, lb, lc = (resolve(x).layout for x in (a, b, c))
+    for lay in (la, lb, lc):
+        if T.grid_shape(lay)[1] != 1 or T.replication_factor(lay) != 1:
+            raise ValueError("row_partitioned_matmul expects row-partitioned, unreplicated matrices")
+    return execute_stationary_c(a, b, c, **kwargs)
+
+
 def matmul(a: Any, b: Any, c: Any, *, method: str = "auto", **kwargs) -> list[MultiplyOp]:
     """``C += A @ B`` with ``method`` in {auto, stationary_c, stationary_b}."""
     chosen = P.select_method(method, resolve(b).layout, resolve(c).layout)

@@ -364,3 +364,55 @@ class SignalPad:
         native.check(native.lib().ug_signal_wait(self.buffer.ptr(self.world.rank) + 4 * slot, value, st.status_ptr,
                                                  self.timeout_ns, ctypes.c_void_p(st.stream())), "ug_signal_wait")
         st.launches += 1
+
+
+# ----------------------------------------------------------------------------- redistribute
+def redistribute(dt: Any, partition, replication_factor: int = 1, dtype: torch.dtype | None = None) -> DistMatrix:
+    """Return a copy of the matrix in another partition (collective).
+
+    One-sided: every rank pulls the pieces of the source tiles that overlap its new tile straight from their
+    owners (``ug_pull_2d`` over peer pointers on the GPU), then converts the dtype locally if asked
+    (``ug_convert_2d``).  This is the data movement the plain DTensor path performs with NCCL collectives
+    (``redistribute`` in the reference's benchmark/matmul_bench_worker.py:96-105)."""
+    from .matrix import empty
+
+    src = resolve(dt)
+    world = src.world
+    out = empty(world, src.shape, partition, src.dtype if dtype is None else dtype, replication_factor)
+    staging = out if out.dtype == src.dtype else None
+    mine = T.tile_bounds(out.layout, out.coord)
+    tmp = None
+    if staging is None:
+        tmp = torch.zeros(out.local.shape, dtype=src.dtype, device=src.device)
+    world.device_barrier()                       # the source is complete on every rank
+    if not mine.empty:
+        for coord in T.overlapping_tiles(src.layout, mine):
+            sb = T.tile_bounds(src.layout, coord)
+            inter = T.intersect_2d(sb, mine)
+            if inter.empty:
+                continue
+            owner = T.tile_rank(src.layout, coord, rank=src.rank)
+            local_src = T.subtract_offset(inter, (sb.rows.start, sb.cols.start))
+            local_dst = T.subtract_offset(inter, (mine.rows.start, mine.cols.start))
+            dst_t = (out.local if tmp is None else tmp)[local_dst.rows.as_slice(), local_dst.cols.as_slice()]
+            if not world.is_cuda:
+                dst_t.copy_(src.peer_tile(owner)[local_src.rows.as_slice(), local_src.cols.as_slice()])
+                continue
+            from ..ops.device import DeviceState
+
+            r, c = inter.shape
+            sptr = src.tile_ptr(owner) + (local_src.rows.start * src.ld + local_src.cols.start) * src.itemsize
+            DeviceState.get(src.device).pull_2d(dst_t.data_ptr(), dst_t.stride(0) * src.itemsize, sptr,
+                                                src.ld * src.itemsize, r, c * src.itemsize, src.itemsize)
+    if tmp is not None:
+        if world.is_cuda:
+            from ..ops.device import DeviceState, torch_dtype_code
+
+            rows, cols = tmp.shape
+            if rows and cols:
+                DeviceState.get(src.device).convert_2d(out.local.data_ptr(), out.ld, torch_dtype_code(out.dtype),
+                                                       tmp.data_ptr(), tmp.stride(0), torch_dtype_code(src.dtype), rows, cols)
+        else:
+            out.local.copy_(tmp)
+    world.device_barrier()                       # peers are done reading the source
+    return out
