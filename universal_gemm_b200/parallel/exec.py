@@ -39,6 +39,13 @@ def clear_program_cache() -> None:
     _program_cache.clear()
 
 
+def drop_programs_for(local_ptr: int) -> None:
+    """Forget lowered programs that reference the symmetric buffer at ``local_ptr`` (called when a matrix is
+    freed: a later allocation may get the same local address but different peer mappings)."""
+    for key in [k for k in _program_cache if local_ptr in k[1:4]]:
+        del _program_cache[key]
+
+
 # ----------------------------------------------------------------------------- lowering
 def _owner(dm: DistMatrix, idx: tuple[int, int], replica: int | None = None) -> int:
     return T.tile_rank(dm.layout, idx, replica=replica, rank=dm.rank)

@@ -145,6 +145,10 @@ class DistMatrix:
         return self._dtensor
 
     def free(self) -> None:
+        """Release the symmetric allocation (collective: every rank frees the same matrix in the same order)."""
+        from . import exec as _exec
+
+        _exec.drop_programs_for(self.buffer.ptr(self.rank))
         _registry.pop(self.buffer.ptr(self.rank), None)
         if self._dtensor is not None:
             _registry.pop(id(self._dtensor), None)
