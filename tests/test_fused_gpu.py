@@ -201,13 +201,14 @@ def test_bounded_wait_reports_timeout_instead_of_hanging():
     st = DeviceState.get(_dev())
     slots = torch.zeros(2, 8, dtype=torch.int32, device=_dev())      # "rank 1" never adds to our slot
     table = torch.tensor([slots[0].data_ptr(), slots[1].data_ptr()], dtype=torch.int64, device=_dev())
-    native.check(native.lib().ug_signal_barrier(table.data_ptr(), 2, 0, 1, st.status_ptr, 50_000_000, 0, 0,
+    rounds = torch.zeros(1, dtype=torch.int32, device=_dev())
+    native.check(native.lib().ug_signal_barrier(table.data_ptr(), 2, 0, rounds.data_ptr(), st.status_ptr, 50_000_000, 0, 0,
                                                 ctypes.c_void_p(st.stream())), "ug_signal_barrier")
     torch.cuda.synchronize()
     with pytest.raises(KernelStatusError) as err:
         st.check()
     assert err.value.code == native.ERR_TIMEOUT_PEER
-    assert slots[1, 0].item() == 1                                    # our own signal was delivered
+    assert slots[1, 0].item() == 1 and rounds.item() == 1             # our own signal was delivered
     st.check()                                                        # status cleared, context alive
     assert torch.ones(4, device=_dev()).sum().item() == 4
 
@@ -277,3 +278,25 @@ def test_redistribute_on_gpu():
     torch.cuda.synchronize()
     assert torch.equal(outs[2].full_tensor(), full)
     assert torch.equal(halves[1].full_tensor().float(), full.bfloat16().float())
+
+
+def test_prepared_matmul_and_cuda_graph():
+    """A prepared plan gives the same result eagerly and when replayed from a CUDA graph."""
+    m, n, k = 512, 768, 640
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=12, device=_dev())
+    world = ug.SingleWorld(_dev())
+    a = ug.distribute_tensor(full_a, world, "row", dtype=torch.bfloat16)
+    b = ug.distribute_tensor(full_b, world, "column", dtype=torch.bfloat16)
+    c = ug.distribute_tensor(full_c, world, "row", dtype=torch.float32)
+    plan = ug.prepare_matmul(a, b, c, method="stationary_c", beta=1)
+    plan.run()
+    _status_ok()
+    prod = full_a.bfloat16().double() @ full_b.bfloat16().double()
+    torch.testing.assert_close(c.full_tensor().double(), full_c.double() + prod, rtol=2e-3, atol=2e-3)
+    plan.capture(warmup=1)              # two more accumulations: warm-up + capture run nothing new... capture does not execute
+    torch.cuda.synchronize()
+    before = c.full_tensor().double()
+    for _ in range(3):
+        plan()
+    _status_ok()
+    torch.testing.assert_close(c.full_tensor().double(), before + 3 * prod, rtol=2e-3, atol=4e-3)

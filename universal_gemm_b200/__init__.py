@@ -45,6 +45,7 @@ from .parallel.exec import (  # noqa: F401
     execute_stationary_b, execute_stationary_b_ops, execute_stationary_b_ops_async, execute_stationary_c,
     execute_stationary_c_ops, execute_stationary_c_ops_async, matmul, row_partitioned_matmul,
 )
+from .parallel.prepared import MatmulPlan, prepare_matmul  # noqa: F401
 from .parallel import handler as mm_handler  # noqa: F401
 from .utils import profile  # noqa: F401
 

@@ -3,7 +3,8 @@
 //
 // Rank r owns uint32 slots[world].  A barrier adds 1 to slot r of every peer
 // (red.release.sys over NVLink) and then waits until each of its own slots has
-// reached the barrier's sequence number.  The wait is bounded: when the limit
+// reached the barrier's sequence number (a per-rank device counter that every
+// launch advances, so all ranks agree on it as long as they call in the same order).  The wait is bounded: when the limit
 // runs out the kernel stores UG_ERR_TIMEOUT_PEER in the status word and returns,
 // so the context stays usable and the host can raise.
 //
@@ -23,8 +24,14 @@ namespace {
 constexpr int kBarrierThreads = 256;
 
 __global__ void __launch_bounds__(kBarrierThreads) signal_barrier_kernel(
-    const uint64_t* __restrict__ peer_slots, int world, int rank, uint32_t seq, uint32_t* status,
+    const uint64_t* __restrict__ peer_slots, int world, int rank, uint32_t* seq_counter, uint32_t* status,
     uint64_t timeout_ns, uint32_t* clear_ptr, int num_clear) {
+  // The barrier's sequence number lives in device memory and advances by one per launch, so a captured
+  // launch can be replayed (a CUDA graph of barrier + GEMM + barrier) and still wait for the right round.
+  __shared__ uint32_t s_seq;
+  if (threadIdx.x == 0) s_seq = atomicAdd(seq_counter, 1u) + 1u;
+  __syncthreads();
+  const uint32_t seq = s_seq;
   // Plan-local words (chunk counters, piece cursor) go back to zero here, so the
   // fused kernel that follows in the stream starts from a clean slate.
   for (int i = threadIdx.x; i < num_clear; i += blockDim.x) clear_ptr[i] = 0u;
@@ -82,12 +89,12 @@ extern "C" int ug_signal_wait(uint64_t counter, uint32_t expected, uint64_t stat
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int ug_signal_barrier(const uint64_t* peer_slots_dev, int world, int rank, uint32_t seq,
+extern "C" int ug_signal_barrier(const uint64_t* peer_slots_dev, int world, int rank, uint64_t seq_counter,
                                  uint64_t status, uint64_t timeout_ns, uint64_t clear_ptr, int num_clear,
                                  void* stream) {
   if (world <= 0 || rank < 0 || rank >= world) return static_cast<int>(cudaErrorInvalidValue);
   signal_barrier_kernel<<<1, kBarrierThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      peer_slots_dev, world, rank, seq, reinterpret_cast<uint32_t*>(status), timeout_ns,
+      peer_slots_dev, world, rank, reinterpret_cast<uint32_t*>(seq_counter), reinterpret_cast<uint32_t*>(status), timeout_ns,
       reinterpret_cast<uint32_t*>(clear_ptr), num_clear);
   return static_cast<int>(cudaGetLastError());
 }

@@ -116,10 +116,11 @@ int ug_fused_gemm_pair_max_pairs(void);
 int ug_fused_gemm_smem_bytes(void);
 
 // Cross-rank barrier on symmetric counters.  `peer_slots[p]` is the address (in
-// this process) of rank p's counter array uint32[world]; the kernel adds 1 to
-// slot `rank` of every peer and waits until its own slots reach `seq`.
+// this process) of rank p's counter array uint32[world]; the kernel advances the
+// local uint32 at `seq_counter`, adds 1 to slot `rank` of every peer and waits until
+// its own slots reach the new sequence number.
 // Also zeroes `num_clear` uint32 words at `clear_ptr` (plan flags) when non-zero.
-int ug_signal_barrier(const uint64_t* peer_slots_dev, int world, int rank, uint32_t seq,
+int ug_signal_barrier(const uint64_t* peer_slots_dev, int world, int rank, uint64_t seq_counter,
                       uint64_t status, uint64_t timeout_ns, uint64_t clear_ptr, int num_clear,
                       void* stream);
 // Point-to-point signals: add `value` to a uint32 counter (possibly in a peer's memory) after all earlier

@@ -116,7 +116,7 @@ def lib() -> ctypes.CDLL:
     L.ug_fused_gemm_pair.argtypes = [POINTER(FusedParams), c_int, c_void_p]
     L.ug_fused_gemm_pair.restype = c_int
     L.ug_fused_gemm_pair_max_pairs.restype = c_int
-    L.ug_signal_barrier.argtypes = [c_uint64, c_int, c_int, c_uint32, c_uint64, c_uint64, c_uint64, c_int,
+    L.ug_signal_barrier.argtypes = [c_uint64, c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int,
                                     c_void_p]
     L.ug_zero_2d.argtypes = [c_uint64, c_int64, c_int32, c_int64, c_void_p]
     L.ug_signal_add.argtypes = [c_uint64, c_uint32, c_void_p]

@@ -194,7 +194,7 @@ class CudaIpcWorld(World):
         self._signal.local.zero_()
         self._slots = torch.tensor([self._signal.ptr(r) for r in range(self.size)], dtype=torch.int64,
                                    device=self.device)
-        self._seq = 0
+        self._seq = torch.zeros(1, dtype=torch.int32, device=self.device)     # barrier round, advanced on the device
         torch.cuda.synchronize(self.device)
         self.barrier()
 
@@ -243,10 +243,9 @@ class CudaIpcWorld(World):
         self.comm.barrier()
 
     def device_barrier(self, clear_ptr: int = 0, num_clear: int = 0) -> int:
-        self._seq += 1
         L = self._native.lib()
         self._native.check(
-            L.ug_signal_barrier(self._slots.data_ptr(), self.size, self.rank, self._seq & 0xFFFFFFFF,
+            L.ug_signal_barrier(self._slots.data_ptr(), self.size, self.rank, self._seq.data_ptr(),
                                 self.state.status_ptr, self.timeout_ns, clear_ptr, num_clear,
                                 ctypes.c_void_p(self.state.stream())), "ug_signal_barrier")
         self.state.launches += 1
