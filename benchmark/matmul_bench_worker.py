@@ -104,8 +104,12 @@ def bench_case(world, args: argparse.Namespace) -> BenchResult | None:
             executed = ug.select_method(args.method, b.layout, c.layout)
             mats = (a, b, c)
 
-            def iteration():
-                ug.matmul(a, b, c, method=executed, beta=0)     # C = A @ B, like "zero C; C += A @ B"
+            if world.is_cuda and getattr(args, "cuda_graph", False) and in_dtype == torch.bfloat16:
+                plan = ug.prepare_matmul(a, b, c, method=executed, beta=0).capture()
+                iteration = plan.run                              # barrier + fused GEMM + barrier from a CUDA graph
+            else:
+                def iteration():
+                    ug.matmul(a, b, c, method=executed, beta=0)  # C = A @ B, like "zero C; C += A @ B"
 
         for _ in range(args.warmup_iters):
             iteration()
@@ -201,6 +205,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--device", choices=["cuda", "cpu"], default="cuda" if torch.cuda.is_available() else "cpu")
     p.add_argument("--b-scale", type=float, default=1.0)
     p.add_argument("--verify", action="store_true", help="compare the result with an fp64 matmul of the full matrices")
+    p.add_argument("--cuda-graph", action="store_true", help="replay each stationary GEMM from a captured CUDA graph")
     args = p.parse_args(argv)
     for name in ("a_partition", "b_partition", "c_partition"):
         setattr(args, name, ug.parallel.partition.normalize_partition(getattr(args, name)))

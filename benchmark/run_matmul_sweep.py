@@ -82,6 +82,7 @@ def main() -> None:
     ap.add_argument("--device", choices=["cuda", "cpu"], default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--theoretical-tflops", type=float, default=None)
     ap.add_argument("--verify", action="store_true")
+    ap.add_argument("--cuda-graph", action="store_true", help="replay each stationary GEMM from a captured CUDA graph")
     ap.add_argument("--max-cases", type=int, default=0)
     ap.add_argument("--only-methods", default="", help="comma-separated filter applied to the case list")
     ap.add_argument("--max-m", type=int, default=0, help="skip shapes with more rows than this (0 = no limit)")
@@ -117,7 +118,7 @@ def main() -> None:
             warmup_iters=args.warmup_iters, measure_iters=args.measure_iters, seed=args.seed + idx,
             theoretical_tflops=args.theoretical_tflops, dtype=args.dtype or ("bf16" if args.device == "cuda" else "fp32"),
             c_dtype=args.c_dtype, device=args.device, b_scale=1.0 / max(shape.k, 1) ** 0.5, verify=args.verify,
-            result_file="")
+            result_file="", cuda_graph=args.cuda_graph)
         ok = torch.ones(1, device=world.device)
         try:
             rec = worker.bench_case(world, ns)

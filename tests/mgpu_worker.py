@@ -93,6 +93,34 @@ def main() -> int:
         world.barrier()
         for mat in (a, b, c):
             mat.free()
+    # prepared plan replayed from a CUDA graph (GPU only): barriers keep their round counter on the device
+    if dev.type == "cuda":
+        m, n, k = 384, 512, 448
+        g = torch.Generator().manual_seed(11)
+        full_a, full_b = torch.randn(m, k, generator=g).to(dev), (torch.randn(k, n, generator=g) / 20).to(dev)
+        a = ug.distribute_tensor(full_a, world, "row", dtype=in_dtype)
+        b = ug.distribute_tensor(full_b, world, "row", dtype=in_dtype)          # K split: Stationary-B adds atomically
+        c = ug.zeros(world, (m, n), "row", torch.float32)
+        plan = ug.prepare_matmul(a, b, c, method="stationary_b", beta=1).capture()
+        torch.cuda.synchronize()
+        world.barrier()
+        c.local_padded.zero_()
+        torch.cuda.synchronize()
+        world.barrier()
+        for _ in range(4):
+            plan()
+        torch.cuda.synchronize()
+        ug.check_status(dev)
+        world.barrier()
+        got = c.full_tensor().double()
+        torch.cuda.synchronize()
+        want = 4 * (full_a.to(in_dtype).double() @ full_b.to(in_dtype).double())
+        ncases += 1
+        if (got - want).abs().max().item() > 3e-3 * max(1.0, want.abs().max().item()):
+            failures += 1
+            print(f"[rank {rank}] FAIL cuda-graph replay", flush=True)
+        world.barrier()
+
     # torch.addmm(c, a, b, out=c) on DTensors through the dispatch hook
     m, n, k = 96, 80, 72
     g = torch.Generator().manual_seed(7)
