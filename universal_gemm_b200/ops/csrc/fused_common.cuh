@@ -140,82 +140,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Write 32 consecutive accumulator columns of one row.  `ncols` (1..32) of them are
-// inside the region.  `p` points at the first of them.
-__device__ __forceinline__ void store_row_f32(float* p, const uint32_t (&v)[32], int ncols, int mode,
-                                              bool vec) {
-  if (vec && ncols == 32) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float a = __uint_as_float(v[4 * j + 0]), b = __uint_as_float(v[4 * j + 1]);
-      float c = __uint_as_float(v[4 * j + 2]), d = __uint_as_float(v[4 * j + 3]);
-      float4* q = reinterpret_cast<float4*>(p + 4 * j);
-      if (mode == 1) {
-        red_add_v4_f32(q, a, b, c, d);
-      } else {
-        if (mode == 0) {
-          float4 old = *q;
-          a += old.x; b += old.y; c += old.z; d += old.w;
-        }
-        *q = make_float4(a, b, c, d);
-      }
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (j < ncols) {
-        float a = __uint_as_float(v[j]);
-        if (mode == 1) red_add_f32(p + j, a);
-        else if (mode == 0) p[j] += a;
-        else p[j] = a;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* p, const uint32_t (&v)[32], int ncols,
-                                               int mode, bool vec) {
-  if (vec && ncols == 32) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float f[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * j + e]);
-      uint4* q = reinterpret_cast<uint4*>(p + 8 * j);
-      if (mode == 1) {
-        red_add_v4_bf16x2(q, pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
-                          pack_bf16x2(f[6], f[7]));
-      } else {
-        if (mode == 0) {
-          uint4 old = *q;
-          const __nv_bfloat162* o = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float2 of = __bfloat1622float2(o[e]);
-            f[2 * e] += of.x;
-            f[2 * e + 1] += of.y;
-          }
-        }
-        uint4 out;
-        out.x = pack_bf16x2(f[0], f[1]); out.y = pack_bf16x2(f[2], f[3]);
-        out.z = pack_bf16x2(f[4], f[5]); out.w = pack_bf16x2(f[6], f[7]);
-        *q = out;
-      }
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (j < ncols) {
-        float a = __uint_as_float(v[j]);
-        if (mode == 1) atomicAdd(p + j, __float2bfloat16_rn(a));
-        else if (mode == 0) p[j] = __float2bfloat16_rn(__bfloat162float(p[j]) + a);
-        else p[j] = __float2bfloat16_rn(a);
-      }
-    }
-  }
-}
-
-// Coalesced variant for full, 16-byte aligned chunks: the warp's 32 x 32 block goes through a
+// Full, 16-byte aligned chunks: the warp's 32 x 32 block of accumulators goes through a
 // shared-memory buffer so that each store / reduction instruction covers whole 128-byte row
 // segments (4 rows of fp32, 8 rows of bf16) instead of 32 different rows.  This matters most for
 // red.add into a peer's memory, where every instruction becomes a few full NVLink packets.
@@ -366,7 +291,7 @@ __device__ __forceinline__ void store_chunk_scalar(float* sb, const uint32_t (&v
 }
 
 // ---------------------------------------------------------------- fetch warps
-// Copy one piece with the 32 lanes of a warp.  mode 0: 16-byte vectors, eight in
+// Copy one piece with the 32 lanes of a warp.  mode 0: 16-byte vectors, sixteen in
 // flight per lane.  mode 1: the source is only 2-byte aligned; every 16-byte
 // destination vector is gathered from eight 2-byte loads.
 __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {

@@ -4,7 +4,7 @@
 //     C_region (+)= sum_s  A_slice[s] @ B_slice[s]
 // that the host lowered from a Stationary-B / Stationary-C plan.  Per CTA:
 //
-//   warp 0      TMA producer: waits for staged chunks, fills a 4-deep smem ring
+//   warp 0      TMA producer: waits for staged chunks, fills the smem ring (4 or 3 stages)
 //               (A 128x64 K-major, B 64x256 N-major, 128-byte swizzle).
 //   warp 1      UMMA issuer: tcgen05.mma 128x256x16 bf16 -> fp32 accumulators in
 //               TMEM (two 256-column buffers, so the epilogue of tile i overlaps
@@ -12,7 +12,7 @@
 //   warps 2-5   epilogue: tcgen05.ld -> registers -> C.  C may live in a peer's
 //               memory; then the partial tile is pushed with red.global.add
 //               (the remote accumulate of Stationary-B and of replica reduction).
-//   warps 6-9   fetch warps: copy remote (peer memory, plain P2P loads) or
+//   warps 6-13  fetch warps: copy remote (peer memory, plain P2P loads) or
 //               misaligned operand slices into a local staging buffer, piece by
 //               piece, and bump a per-chunk counter; the producer of whichever
 //               CTA needs the chunk waits on that counter before its TMA loads.
