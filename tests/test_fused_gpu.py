@@ -123,6 +123,13 @@ def test_tile_kernels():
     st.convert_2d(h.data_ptr(), 64, native.DT_BF16, f.data_ptr(), 47, native.DT_F32, 33, 47)
     torch.cuda.synchronize()
     assert torch.equal(h[:, :47], f.bfloat16())
+    f2 = torch.randn(40, 96, device=_dev())                       # aligned: the 16-byte vector kernels
+    h2 = torch.zeros(40, 128, device=_dev(), dtype=torch.bfloat16)
+    st.convert_2d(h2.data_ptr(), 128, native.DT_BF16, f2.data_ptr(), 96, native.DT_F32, 40, 96)
+    back = torch.zeros(40, 96, device=_dev())
+    st.convert_2d(back.data_ptr(), 96, native.DT_F32, h2.data_ptr(), 128, native.DT_BF16, 40, 96)
+    torch.cuda.synchronize()
+    assert torch.equal(h2[:, :96], f2.bfloat16()) and torch.equal(back, f2.bfloat16().float()) and h2[:, 96:].abs().sum() == 0
 
 
 @pytest.mark.parametrize("world,rep", [(1, 1), (2, 1), (4, 2), (8, 1), (8, 2), (8, 4)])
