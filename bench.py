@@ -49,6 +49,8 @@ def parse_args(argv=None):
     ap.add_argument("--c-dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--profile", action="store_true", help="add a per-step device-time breakdown (barriers vs fused kernel)")
+    ap.add_argument("--trace-dir", default="", help="after the timed region, run one more step with the in-kernel "
+                    "timeline on and write trace_rank<r>_*.json there")
     ap.add_argument("--master-port", type=int, default=29517)
     return ap.parse_args(argv)
 
@@ -194,6 +196,14 @@ def run_ours(args) -> dict:
             allv = [mine]
         breakdown = {"barrier_ms_per_rank": [round(float(v[0]), 4) for v in allv],
                      "fused_kernel_ms_per_rank": [round(float(v[1]), 4) for v in allv]}
+
+    if args.trace_dir:
+        ug.trace.attach_cached()
+        sync_all(world)
+        step()
+        sync_all(world)
+        ug.trace.dump(args.trace_dir, rank=world.rank, chrome=world.rank == 0)
+        ug.trace.detach_all()
 
     flops = 2.0 * m * n * k
     value = flops / (ms_per_step * 1e-3) / 1e12

@@ -41,6 +41,7 @@ def main() -> None:
     ap.add_argument("--beta", type=int, default=0)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--trace-dir", default="", help="after timing, run one traced launch and write its timeline here")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     m, n, k = args.dim_m, args.dim_n, args.dim_k
@@ -78,8 +79,22 @@ def main() -> None:
     ms = e0.elapsed_time(e1) / args.iters
     prog, _ = X._program(kind, a, b, c, ops, True, args.beta)
     flops = 2.0 * m * n * k / args.world
+    timeline = None
+    if args.trace_dir:
+        from universal_gemm_b200.utils import trace as TR
+
+        prog.enable_trace()
+        run()
+        arr = prog.read_trace()
+        timeline = TR.summarize(arr, pair=bool(prog.params.cta_pair))
+        os.makedirs(args.trace_dir, exist_ok=True)
+        tag = f"{kind}_w{args.world}_r{args.rank}_{m}x{n}x{k}_{prog.stats['tile_m']}"
+        with open(os.path.join(args.trace_dir, f"timeline_{tag}.json"), "w", encoding="utf-8") as f:
+            json.dump({"summary": timeline, "stats": prog.stats,
+                       "traceEvents": TR.to_chrome_trace(arr, pid=args.rank, label=tag)}, f)
+        prog.disable_trace()
     print(json.dumps({"world": args.world, "rank": args.rank, "method": "stationary_" + kind, "m": m, "n": n, "k": k,
-                      "ms_per_call": ms, "rank_tflops": flops / ms / 1e9, "program": prog.stats}))
+                      "ms_per_call": ms, "rank_tflops": flops / ms / 1e9, "program": prog.stats, "timeline": timeline}))
 
 
 if __name__ == "__main__":

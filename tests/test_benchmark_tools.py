@@ -61,3 +61,30 @@ def test_suite_runner_resume_and_report(tmp_path):
     assert proc.returncode == 0
     html = (out / "report.html").read_text()
     assert "stationary_c | A=row B=column C=row | rep=1" in html and "method-toggle" in html and "<svg" not in html[:100]
+
+
+def test_trace_summary_on_a_synthetic_timeline():
+    """utils.trace.summarize / to_chrome_trace on a hand-made two-CTA timeline (no GPU involved)."""
+    import numpy as np
+
+    from universal_gemm_b200.utils import trace as TR
+
+    arr = np.zeros((2, 3, 8), dtype=np.int64)          # 2 CTAs, 2 tile slots + summary
+    base = 1_000_000
+    for cta in range(2):
+        arr[cta, 2, TR.S_START] = base + 100 * cta
+        arr[cta, 2, TR.S_END] = base + 50_000
+        arr[cta, 2, TR.S_FETCH_END] = base + 9_000
+        arr[cta, 2, TR.S_PIECES] = 3 + cta
+        for i in range(2):
+            t = base + 1_000 + i * 20_000
+            arr[cta, i] = [cta + 2 * i + 1, t, 500 * i, t + 15_000, t + 1_000, t + 16_000, t + 18_000, t + 19_000 + cta * 1_000]
+    s = TR.summarize(arr)
+    assert s["recorded_tiles"] == 4 and s["pieces_copied"] == 7
+    assert abs(s["kernel_us"] - 50.0) < 1e-9 and abs(s["cta_start_spread_us"] - 0.1) < 1e-9
+    assert abs(s["main_us_mean"] - 17.0) < 1e-9 and s["main_us_by_iteration"] == [17.0, 17.0]
+    assert s["flagwait_us_by_iteration"] == [0.0, 0.5] and abs(s["flagwait_us_max_per_cta"] - 0.5) < 1e-9
+    assert abs(s["cta_finish_spread_us"] - 1.0) < 1e-9 and abs(s["fetch_end_us"] - 9.0) < 1e-9
+    ev = TR.to_chrome_trace(arr, pid=3)
+    assert {e["name"] for e in ev} == {"load", "main", "epilogue", "fetch"} and all(e["pid"] == 3 for e in ev)
+    assert TR.summarize(np.zeros((2, 3, 8), dtype=np.int64)) == {"grid": 2, "recorded_tiles": 0}

@@ -47,7 +47,7 @@ from .parallel.exec import (  # noqa: F401
 )
 from .parallel.prepared import MatmulPlan, prepare_matmul  # noqa: F401
 from .parallel import handler as mm_handler  # noqa: F401
-from .utils import profile  # noqa: F401
+from .utils import profile, trace  # noqa: F401
 
 
 def init(backend: str | None = None, device=None, timeout_s: float = 10.0) -> World:

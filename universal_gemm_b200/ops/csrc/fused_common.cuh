@@ -35,6 +35,25 @@ __device__ __forceinline__ void raise_error(const WaitCtl& ctl, uint32_t code) {
   *ctl.abort = 1u;
 }
 
+// Optional timeline (UgFusedParams::trace != 0): one 64-byte record per (CTA, tile iteration), written by
+// single threads with plain stores; the host reads it after the kernel.  Costs one uniform branch when off.
+__device__ __forceinline__ uint64_t* trace_slot(const UgFusedParams& P, int cta, int iter) {
+  if (P.trace == 0 || iter > P.trace_slots) return nullptr;
+  return reinterpret_cast<uint64_t*>(P.trace) + (static_cast<int64_t>(cta) * (P.trace_slots + 1) + iter) * 8;
+}
+__device__ __forceinline__ void trace_put(const UgFusedParams& P, int cta, int iter, int field, uint64_t v) {
+  if (P.trace == 0 || iter >= P.trace_slots) return;
+  trace_slot(P, cta, iter)[field] = v;
+}
+__device__ __forceinline__ void trace_now(const UgFusedParams& P, int cta, int iter, int field) {
+  if (P.trace == 0 || iter >= P.trace_slots) return;
+  trace_slot(P, cta, iter)[field] = global_timer_ns();
+}
+// Summary record of the CTA (index trace_slots).
+__device__ __forceinline__ uint64_t* trace_summary(const UgFusedParams& P, int cta) {
+  return P.trace == 0 ? nullptr : trace_slot(P, cta, P.trace_slots);
+}
+
 // Bounded mbarrier wait.  Returns false after an abort or a timeout.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtl& ctl) {
   uint32_t spins = 0;

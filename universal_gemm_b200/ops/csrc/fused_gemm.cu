@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     }
     sh->abort = 0;
     fence_mbar_init();
+    if (uint64_t* ts = trace_summary(P, blockIdx.x)) ts[UG_TR_S_START] = global_timer_ns();
   }
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&sh->tmem_base), kTmemCols);
@@ -113,15 +114,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       uint32_t stage = 0, phase = 0;
       uint64_t seen[4] = {0, 0, 0, 0};   // tensor maps already acquired by this thread
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x) {
+      int iter = 0;
+      for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x, ++iter) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
         const int tile_n = task_tile_n(t);
         const int n_rem = min(tile_n, t.n - tc.nt * tile_n);
         const int n_chunks = min(4, (n_rem + 63) >> 6);
         const uint32_t tx_bytes = kABytes + n_chunks * kBChunkBytes;
+        trace_put(P, blockIdx.x, iter, UG_TR_TILE, static_cast<uint64_t>(tile) + 1u);
+        trace_now(P, blockIdx.x, iter, UG_TR_PROD_BEGIN);
+        uint64_t waited = 0;
         for (int s = 0; ok && s < t.seg_count; ++s) {
           const UgSegment& sg = segs[t.seg_begin + s];
+          const uint64_t w0 = (P.trace != 0 && (sg.a_flag >= 0 || sg.b_flag >= 0)) ? global_timer_ns() : 0;
           if (sg.a_flag >= 0) {
             const int f = sg.a_flag + tc.mt;
             ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
@@ -131,6 +137,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
             ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
           }
           if (!ok) break;
+          if (w0 != 0) waited += global_timer_ns() - w0;
           if (sg.a_flag >= 0 || sg.b_flag >= 0) fence_proxy_async();
           const uint64_t amap = P.maps + static_cast<uint64_t>(sg.a_map) * 128u;
           const uint64_t bmap = P.maps + static_cast<uint64_t>(sg.b_map) * 128u;
@@ -165,6 +172,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
         }
+        trace_put(P, blockIdx.x, iter, UG_TR_PROD_FLAGWAIT, waited);
+        trace_now(P, blockIdx.x, iter, UG_TR_PROD_END);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -172,7 +181,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x) {
+      int iter = 0;
+      for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x, ++iter) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
         const int n_rem = min(task_tile_n(t), t.n - tc.nt * task_tile_n(t));
@@ -180,6 +190,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
         ok = mbar_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1u, ctl);
         if (!ok) break;
         tc_fence_after();
+        trace_now(P, blockIdx.x, iter, UG_TR_MMA_BEGIN);
         const uint32_t d_tmem = tmem_base + (C::kAccBufs == 2 ? acc * UG_BN : 0u);
         for (int kb = 0; kb < t.kblocks; ++kb) {
           ok = mbar_wait(smem_u32(&sh->full[stage]), phase, ctl);
@@ -201,6 +212,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
         }
         if (!ok) break;
         umma_commit(smem_u32(&sh->acc_full[acc]));
+        trace_now(P, blockIdx.x, iter, UG_TR_MMA_ISSUED);
         if (C::kAccBufs == 2) acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -211,12 +223,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + quad * (kEpiWarpBytes / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x) {
+    int iter = 0;
+    for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x, ++iter) {
       const TileCoord tc = locate(tasks, P.num_tasks, tile);
       const UgTask& t = tasks[tc.task];
       ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
       if (!ok) break;
       tc_fence_after();
+      if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
       const int col0 = tc.nt * task_tile_n(t);
       const int n_rem = min(task_tile_n(t), t.n - col0);
 #pragma unroll
@@ -257,6 +271,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
           }
         }
       }
+      if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->acc_empty[acc]));
       if (C::kAccBufs == 2) acc ^= 1u;
@@ -267,6 +282,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     const UgPiece* __restrict__ pieces = reinterpret_cast<const UgPiece*>(P.pieces);
     uint32_t* counter = reinterpret_cast<uint32_t*>(P.piece_counter);
     uint32_t* wflags = reinterpret_cast<uint32_t*>(P.flags);
+    unsigned long long copied = 0;
     while (P.num_pieces > 0) {
       uint32_t p = 0;
       if (lane == 0) p = atomicAdd(counter, 1u);
@@ -279,6 +295,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       if (lane == 0) {
         __threadfence();
         red_release_gpu_add(wflags + pc.flag, 1u);
+      }
+      ++copied;
+    }
+    if (lane == 0 && P.num_pieces > 0) {
+      if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
+        atomicMax(reinterpret_cast<unsigned long long*>(ts + UG_TR_S_FETCH_END),
+                  static_cast<unsigned long long>(global_timer_ns()));
+        atomicAdd(reinterpret_cast<unsigned long long*>(ts + UG_TR_S_PIECES), copied);
       }
     }
   }
@@ -293,6 +317,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
   __syncthreads();
   tc_fence_after();
   if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0) {
+    if (uint64_t* ts = trace_summary(P, blockIdx.x)) ts[UG_TR_S_END] = global_timer_ns();
+  }
 }
 
 }  // namespace

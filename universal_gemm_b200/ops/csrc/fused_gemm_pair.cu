@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     }
     sh->abort = 0;
     fence_mbar_init();
+    if (uint64_t* ts = trace_summary(P, blockIdx.x)) ts[UG_TR_S_START] = global_timer_ns();
   }
   if (warp == kMmaWarp) {
     tmem_alloc_pair(smem_u32(&sh->tmem_base), kTmemCols);
@@ -93,13 +94,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       uint32_t stage = 0, phase = 0;
       uint64_t seen[4] = {0, 0, 0, 0};
       bool ok = true;
-      for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs) {
+      int iter = 0;
+      for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs, ++iter) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
         const int tile_n = task_tile_n(t);               // 256, or 128 for tail tiles: 128 / 64 columns per CTA
         const int cta_cols = tile_n >> 1;
+        trace_put(P, blockIdx.x, iter, UG_TR_TILE, static_cast<uint64_t>(tile) + 1u);
+        trace_now(P, blockIdx.x, iter, UG_TR_PROD_BEGIN);
+        uint64_t waited = 0;
         for (int s = 0; ok && s < t.seg_count; ++s) {
           const UgSegment& sg = segs[t.seg_begin + s];
+          const uint64_t w0 = (P.trace != 0 && (sg.a_flag >= 0 || sg.b_flag >= 0)) ? global_timer_ns() : 0;
           if (sg.a_flag >= 0) {
             const int f = sg.a_flag + tc.mt;
             ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
@@ -109,6 +115,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
             ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
           }
           if (!ok) break;
+          if (w0 != 0) waited += global_timer_ns() - w0;
           if (sg.a_flag >= 0 || sg.b_flag >= 0) fence_proxy_async();
           const uint64_t amap = P.maps + static_cast<uint64_t>(sg.a_map) * 128u;
           const uint64_t bmap = P.maps + static_cast<uint64_t>(sg.b_map) * 128u;
@@ -138,6 +145,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
             if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
           }
         }
+        trace_put(P, blockIdx.x, iter, UG_TR_PROD_FLAGWAIT, waited);
+        trace_now(P, blockIdx.x, iter, UG_TR_PROD_END);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -145,13 +154,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     if (lane == 0 && rank == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs) {
+      int iter = 0;
+      for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs, ++iter) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
         const uint32_t idesc = make_idesc_pair(static_cast<uint32_t>(task_tile_n(t)));
         ok = mbar_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1u, ctl);
         if (!ok) break;
         tc_fence_after();
+        trace_now(P, blockIdx.x, iter, UG_TR_MMA_BEGIN);
         const uint32_t d_tmem = tmem_base + acc * UG_BN;
         for (int kb = 0; kb < t.kblocks; ++kb) {
           ok = mbar_wait(smem_u32(&sh->full[stage]), phase, ctl);
@@ -172,6 +183,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
         const uint32_t f = smem_u32(&sh->acc_full[acc]);
         umma_commit_pair(mapa_shared(f, 0));
         umma_commit_pair(mapa_shared(f, 1));
+        trace_now(P, blockIdx.x, iter, UG_TR_MMA_ISSUED);
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -182,12 +194,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + quad * (kEpiWarpBytes / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs) {
+    int iter = 0;
+    for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs, ++iter) {
       const TileCoord tc = locate(tasks, P.num_tasks, tile);
       const UgTask& t = tasks[tc.task];
       ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
       if (!ok) break;
       tc_fence_after();
+      if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
       const int col0 = tc.nt * task_tile_n(t);
       const int n_rem = min(task_tile_n(t), t.n - col0);
       const int row0 = tc.mt * 256 + static_cast<int>(rank) * 128 + quad * 32;
@@ -225,6 +239,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
           }
         }
       }
+      if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
       tc_fence_before();
       mbar_arrive_cluster(mapa_shared(smem_u32(&sh->acc_empty[acc]), 0));
       acc ^= 1u;
@@ -235,6 +250,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     const UgPiece* __restrict__ pieces = reinterpret_cast<const UgPiece*>(P.pieces);
     uint32_t* counter = reinterpret_cast<uint32_t*>(P.piece_counter);
     uint32_t* wflags = reinterpret_cast<uint32_t*>(P.flags);
+    unsigned long long copied = 0;
     while (P.num_pieces > 0) {
       uint32_t p = 0;
       if (lane == 0) p = atomicAdd(counter, 1u);
@@ -247,6 +263,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       if (lane == 0) {
         __threadfence();
         red_release_gpu_add(wflags + pc.flag, 1u);
+      }
+      ++copied;
+    }
+    if (lane == 0 && P.num_pieces > 0) {
+      if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
+        atomicMax(reinterpret_cast<unsigned long long*>(ts + UG_TR_S_FETCH_END),
+                  static_cast<unsigned long long>(global_timer_ns()));
+        atomicAdd(reinterpret_cast<unsigned long long*>(ts + UG_TR_S_PIECES), copied);
       }
     }
   }
@@ -261,6 +285,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
   cluster_sync_all();              // neither CTA leaves while the other may still touch its shared memory
   tc_fence_after();
   if (warp == kMmaWarp) tmem_dealloc_pair(tmem_base, kTmemCols);
+  if (threadIdx.x == 0) {
+    if (uint64_t* ts = trace_summary(P, blockIdx.x)) ts[UG_TR_S_END] = global_timer_ns();
+  }
 }
 
 }  // namespace

@@ -84,7 +84,24 @@ typedef struct {
   uint64_t timeout_ns;    // limit of every in-kernel wait
   int32_t prefetch_kblocks;  // L2 prefetch distance of the TMA producer in K blocks (0 = off)
   int32_t cta_pair;          // 1: tables were lowered for the CTA-pair kernel (ug_fused_gemm_pair)
+  uint64_t trace;            // 0 = off; else uint64[grid][trace_slots + 1][8] timeline records (see UG_TR_*)
+  int32_t trace_slots;       // tile iterations recorded per CTA (later ones are dropped)
+  int32_t reserved;
 } UgFusedParams;
+
+// Fields of one timeline record (globaltimer nanoseconds unless noted).  Record `trace_slots` of a CTA is
+// its summary: UG_TR_S_*.
+enum {
+  UG_TR_TILE = 0,        // linear tile index + 1
+  UG_TR_PROD_BEGIN = 1,  // TMA producer reached the tile
+  UG_TR_PROD_FLAGWAIT = 2,  // nanoseconds the producer waited for staged chunks of this tile
+  UG_TR_PROD_END = 3,    // last load of the tile issued
+  UG_TR_MMA_BEGIN = 4,   // accumulator buffer free, first UMMA may issue (leader CTA only in pair mode)
+  UG_TR_MMA_ISSUED = 5,  // last UMMA of the tile issued
+  UG_TR_EPI_BEGIN = 6,   // accumulator complete (seen by the first epilogue warp)
+  UG_TR_EPI_END = 7,     // first epilogue warp finished its rows
+  UG_TR_S_START = 0, UG_TR_S_FETCH_END = 1, UG_TR_S_END = 2, UG_TR_S_PIECES = 3
+};
 
 // ----------------------------------------------------------------------------
 // Host runtime

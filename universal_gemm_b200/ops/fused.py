@@ -106,6 +106,32 @@ class FusedProgram:
         self.clear_ptr = clear_ptr
         self.num_clear = num_clear
         self.stats = stats
+        self._trace: torch.Tensor | None = None
+
+    # ------------------------------------------------------------------ optional per-tile timeline
+    def enable_trace(self, slots: int | None = None) -> None:
+        """Make later launches record a timeline: one 8 x uint64 record per (CTA, tile iteration) plus a
+        summary record per CTA (layout: ``UG_TR_*`` in ugemm_b200.h).  Each launch overwrites the previous one."""
+        workers = max(self.grid // 2 if self.params.cta_pair else self.grid, 1)
+        if slots is None:
+            slots = (int(self.params.total_tiles) + workers - 1) // workers
+        slots = max(int(slots), 1)
+        self._trace = torch.zeros(self.grid, slots + 1, 8, dtype=torch.int64, device=self.device)
+        self.params.trace = self._trace.data_ptr()
+        self.params.trace_slots = slots
+
+    def disable_trace(self) -> None:
+        self._trace = None
+        self.params.trace = 0
+        self.params.trace_slots = 0
+
+    def read_trace(self):
+        """The timeline of the last launch as a numpy array ``[grid, slots + 1, 8]`` (synchronises the device);
+        ``None`` when tracing is off."""
+        if self._trace is None:
+            return None
+        torch.cuda.synchronize(self.device)
+        return self._trace.cpu().numpy()
 
     @property
     def num_pieces(self) -> int:

@@ -25,7 +25,7 @@ from typing import Any, Sequence
 
 import torch
 
-from ..utils import profile
+from ..utils import profile, trace
 from . import plan as P
 from . import runtime as R
 from . import tiles as T
@@ -121,7 +121,16 @@ def _program(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequen
         return hit[2]
     prog = lower_plan(kind, a, b, c, ops, fuse_replica_reduce=fuse, beta=beta)
     _program_cache[key] = (ops, (a.layout, b.layout, c.layout), prog)
+    trace.register(f"stationary_{kind} rank{c.rank} {a.shape[0]}x{b.shape[1]}x{a.shape[1]} beta{beta}", prog[0])
     return prog
+
+
+def cached_programs() -> list:
+    """``(label, FusedProgram)`` of every lowered plan in the cache (for timeline tracing of programs that exist already)."""
+    out = []
+    for key, (_ops, _layouts, prog) in _program_cache.items():
+        out.append((f"stationary_{key[0]} rank{key[4]} beta{key[6]}", prog[0]))
+    return out
 
 
 def _can_fuse(a: DistMatrix, b: DistMatrix, c: DistMatrix) -> bool:
