@@ -36,7 +36,8 @@ def main() -> None:
     ap.add_argument("--mode", choices=["store", "add", "atomic"], default="store")
     ap.add_argument("--c-dtype", choices=["fp32", "bf16"], default="fp32")
     ap.add_argument("--no-torch", action="store_true")
-    ap.add_argument("--tile-m", type=lambda v: v if v == "pair" else int(v), default=None, help="rows per output tile (default: model)")
+    ap.add_argument("--trace", action="store_true", help="add the in-kernel timeline summary of one more launch")
+    ap.add_argument("--tile-m", type=lambda v: v if v.startswith("pair") else int(v), default=None, help="rows per output tile (default: model)")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     m, n, k = args.m, args.n, args.k
@@ -66,6 +67,14 @@ def main() -> None:
     flops = 2.0 * m * n * k
     out = {"m": m, "n": n, "k": k, "ours_ms": ours, "ours_tflops": flops / ours / 1e9, "stats": prog.stats,
            "mode": args.mode, "c_dtype": args.c_dtype}
+    if args.trace:
+        from universal_gemm_b200.utils import trace as TR
+
+        prog.enable_trace()
+        run_program(prog, dev)
+        tl = TR.summarize(prog.read_trace(), pair=bool(prog.params.cta_pair))
+        out["timeline"] = {k_: (round(v, 2) if isinstance(v, float) else v) for k_, v in tl.items()}
+        prog.disable_trace()
     if not args.no_torch:
         ref = timed(lambda: torch.matmul(a, b))
         out.update({"torch_ms": ref, "torch_tflops": flops / ref / 1e9})

@@ -40,7 +40,7 @@ def test_native_library_is_loaded():
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (512, 1024, 512), (300, 520, 200), (375, 1000, 376),
                                    (64, 4099, 1024), (2048, 4096, 1024), (1, 8, 8)])
 @pytest.mark.parametrize("mode", ["store", "add", "atomic"])
-@pytest.mark.parametrize("tile_m", [128, 256, "pair"])
+@pytest.mark.parametrize("tile_m", [128, 256, "pair", "pair512"])
 def test_gemm_kernel_fp32_out(m, n, k, mode, tile_m):
     from universal_gemm_b200.ops import native
     from universal_gemm_b200.ops.gemm import gemm
@@ -74,7 +74,7 @@ def test_gemm_kernel_bf16_out(mode):
 
 
 @pytest.mark.parametrize("stage_a,stage_b", [(True, False), (False, True), (True, True)])
-@pytest.mark.parametrize("tile_m", [128, 256, "pair"])
+@pytest.mark.parametrize("tile_m", [128, 256, "pair", "pair512"])
 def test_gemm_kernel_segments_and_staging(stage_a, stage_b, tile_m):
     from universal_gemm_b200.ops import native
     from universal_gemm_b200.ops.gemm import build_gemm_program, run_program
@@ -235,7 +235,8 @@ def test_beta_zero_overwrites_without_zeroing(method, triple):
     torch.testing.assert_close(mats[0][2].full_tensor().double(), want, rtol=2e-3, atol=2e-3)
 
 
-@pytest.mark.parametrize("tile_m,m,n", [("pair", 512, 10240 - 17), (256, 512, 19712 - 5), (128, 256, 19712)])
+@pytest.mark.parametrize("tile_m,m,n", [("pair", 512, 10240 - 17), (256, 512, 19712 - 5), (128, 256, 19712),
+                                        ("pair512", 512, 20480 - 17)])
 def test_gemm_kernel_tail_wave_uses_narrow_tiles(tile_m, m, n):
     """Tile counts just above a multiple of the worker count: the trailing tile columns run as 128-wide tiles."""
     from universal_gemm_b200.ops import native
@@ -309,7 +310,7 @@ def test_prepared_matmul_and_cuda_graph():
     torch.testing.assert_close(c.full_tensor().double(), before + 3 * prod, rtol=2e-3, atol=4e-3)
 
 
-@pytest.mark.parametrize("tile_m", [128, 256, "pair"])
+@pytest.mark.parametrize("tile_m", [128, 256, "pair", "pair512"])
 def test_kernel_timeline_records_every_tile(tile_m):
     """With tracing on, every tile leaves a record whose stamps are ordered, the fetch warps account for every
     staged piece, and the result is unchanged."""
@@ -329,7 +330,7 @@ def test_kernel_timeline_records_every_tile(tile_m):
     _status_ok()
     torch.testing.assert_close(c, a.float() @ b.float(), rtol=2e-3, atol=2e-3)
     arr = prog.read_trace()
-    pair = tile_m == "pair"
+    pair = str(tile_m).startswith("pair")
     slots = arr.shape[1] - 1
     tiles = arr[:, :slots]
     leaders = tiles[::2] if pair else tiles

@@ -357,4 +357,57 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
 }
 
 
+// Drain this warp's 32 TMEM lanes x n_rem accumulator columns (first column at `taddr`) into rows row0.. and
+// columns col0.. of the task's C.  The common case (fp32 C, 16-byte aligned, whole 32-column chunks) is software
+// pipelined: the TMEM load of the next chunk is in flight while the current chunk goes through shared memory.
+__device__ __forceinline__ void epilogue_drain(uint32_t taddr, const UgTask& t, int row0, int col0, int n_rem,
+                                               float* epi_buf, int lane) {
+  const int rows_valid = min(32, t.m - row0);               // <= 0 when the warp is past the region
+  if (task_c_vec(t) && t.c_dtype == 0 && (n_rem & 31) == 0) {
+    float* c_row = reinterpret_cast<float*>(t.c_ptr) + static_cast<int64_t>(row0) * t.ldc + col0;
+    uint32_t va[32], vb[32];
+    tmem_ld_32x32(taddr, va);
+    for (int c = 0; c < n_rem; c += 64) {
+      tmem_ld_wait();
+      const bool second = c + 32 < n_rem;
+      if (second) tmem_ld_32x32(taddr + c + 32, vb);
+      store_chunk_f32(epi_buf, va, lane, c_row + c, t.ldc, rows_valid, t.c_mode);
+      if (second) {
+        tmem_ld_wait();
+        if (c + 64 < n_rem) tmem_ld_32x32(taddr + c + 64, va);
+        store_chunk_f32(epi_buf, vb, lane, c_row + c + 32, t.ldc, rows_valid, t.c_mode);
+      }
+    }
+    return;
+  }
+  for (int c = 0; c < n_rem; c += 32) {
+    if (t.c_dtype == 1 && task_c_vec(t) && n_rem - c >= 64) {
+      // bf16 output: two 32-column loads make one 128-byte row segment per row
+      uint32_t v0[32], v1[32];
+      tmem_ld_32x32(taddr + c, v0);
+      tmem_ld_32x32(taddr + c + 32, v1);
+      tmem_ld_wait();
+      store_chunk_bf16_64(epi_buf, v0, v1, lane,
+                          reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + static_cast<int64_t>(row0) * t.ldc + col0 + c,
+                          t.ldc, rows_valid, t.c_mode);
+      c += 32;
+      continue;
+    }
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + c, v);
+    tmem_ld_wait();
+    const int ncols = min(32, n_rem - c);
+    const int64_t off0 = static_cast<int64_t>(row0) * t.ldc + col0 + c;
+    if (task_c_vec(t) && ncols == 32) {
+      if (t.c_dtype == 0)
+        store_chunk_f32(epi_buf, v, lane, reinterpret_cast<float*>(t.c_ptr) + off0, t.ldc, rows_valid, t.c_mode);
+      else
+        store_chunk_bf16(epi_buf, v, lane, reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off0, t.ldc, rows_valid,
+                         t.c_mode);
+    } else {
+      store_chunk_scalar(epi_buf, v, lane, t.c_ptr, off0, t.ldc, rows_valid, ncols, t.c_mode, t.c_dtype);
+    }
+  }
+}
+
 }  // namespace ugfused

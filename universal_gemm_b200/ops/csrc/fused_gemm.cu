@@ -238,38 +238,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
         if (tc.mt * BM + h * 128 >= t.m) break;       // whole half outside the region (warp-uniform)
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                (C::kAccBufs == 2 ? acc * UG_BN : static_cast<uint32_t>(h) * UG_BN);
-        for (int c = 0; c < n_rem; c += 32) {
-          if (t.c_dtype == 1 && task_c_vec(t) && n_rem - c >= 64) {
-            // bf16 output: two 32-column loads make one 128-byte row segment per row
-            uint32_t v0[32], v1[32];
-            tmem_ld_32x32(taddr + c, v0);
-            tmem_ld_32x32(taddr + c + 32, v1);
-            tmem_ld_wait();
-            const int r0w = tc.mt * BM + h * 128 + quad * 32;
-            store_chunk_bf16_64(epi_buf, v0, v1, lane,
-                                reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + static_cast<int64_t>(r0w) * t.ldc + col0 + c,
-                                t.ldc, min(32, t.m - r0w), t.c_mode);
-            c += 32;
-            continue;
-          }
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-          const int ncols = min(32, n_rem - c);
-          const int row0 = tc.mt * BM + h * 128 + quad * 32;          // first row of this warp
-          if (task_c_vec(t) && ncols == 32) {
-            const int rows_valid = min(32, t.m - row0);               // <= 0 when the warp is past the region
-            const int64_t off0 = static_cast<int64_t>(row0) * t.ldc + col0 + c;
-            if (t.c_dtype == 0)
-              store_chunk_f32(epi_buf, v, lane, reinterpret_cast<float*>(t.c_ptr) + off0, t.ldc, rows_valid, t.c_mode);
-            else
-              store_chunk_bf16(epi_buf, v, lane, reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off0, t.ldc, rows_valid,
-                               t.c_mode);
-          } else {
-            store_chunk_scalar(epi_buf, v, lane, t.c_ptr, static_cast<int64_t>(row0) * t.ldc + col0 + c, t.ldc,
-                               min(32, t.m - row0), ncols, t.c_mode, t.c_dtype);
-          }
-        }
+        epilogue_drain(taddr, t, tc.mt * BM + h * 128 + quad * 32, col0, n_rem, epi_buf, lane);
       }
       if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
       tc_fence_before();

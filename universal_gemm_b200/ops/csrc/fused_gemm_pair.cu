@@ -7,6 +7,9 @@
 //   * each CTA's TMEM holds its 128 rows x 256 columns, i.e. only half of TMEM, so the accumulators are
 //     double buffered and the epilogue (which may push over NVLink) hides behind the next main loop,
 //     like the one-CTA 128-row tile.
+// A second instantiation (kWide) computes 256 x 512 tiles: each CTA loads 128 rows of A and 2 x 128 columns of B
+// per K block (48 KiB per stage, 4 stages), so an SM needs 48 operand bytes per tensor cycle and every byte in
+// flight feeds twice the tensor time; its 128 x 512 accumulators fill TMEM, so the epilogue is not hidden.
 // CTA rank 0 of the pair issues the UMMAs; TMA loads of both CTAs complete on rank 0's "full" barrier
 // (cp.async.bulk.tensor with .cta_group::2, never multicast); UMMA completion is committed to the
 // "empty" / "accumulator full" barriers of both CTAs with two plain commits.
@@ -22,12 +25,19 @@ using namespace ugfused;
 
 namespace {
 
-constexpr int kPairStages = 6;
+constexpr int kPairStages = 6;                                  // most stages of any instantiation
 constexpr uint32_t kPairABytes = 128 * UG_BK * 2;               // 16 KiB: this CTA's 128 rows of A
-constexpr uint32_t kPairBBytes = 2 * kBChunkBytes;              // 16 KiB: this CTA's 128 columns of B
-constexpr uint32_t kPairStageBytes = kPairABytes + kPairBBytes; // 32 KiB
-constexpr uint32_t kPairRingBytes = kPairStages * kPairStageBytes;
+constexpr uint32_t kPairHalfBBytes = 2 * kBChunkBytes;          // 16 KiB: this CTA's 128 columns of one 256-column UMMA
+constexpr uint32_t kPairRingBytes = 6 * (kPairABytes + kPairHalfBBytes);   // 192 KiB = 4 x 48 KiB as well
 constexpr uint32_t kPairSmemBytes = kPairRingBytes + 1024 + 256 + kEpiBytes;
+
+template <bool kWide>
+struct PairCfg {
+  static constexpr int kStages = kWide ? 4 : 6;
+  static constexpr uint32_t kStageBytes = kPairABytes + (kWide ? 2u : 1u) * kPairHalfBBytes;   // 48 / 32 KiB
+  static constexpr int kAccBufs = kWide ? 1 : 2;
+  static_assert(kStages * kStageBytes == kPairRingBytes, "ring size");
+};
 
 struct PairShared {
   uint64_t full[kPairStages];     // used in rank 0: bytes of both CTAs' loads
@@ -43,7 +53,11 @@ __device__ __forceinline__ uint32_t make_idesc_pair(uint32_t n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((n >> 3) << 17) | ((256u >> 4) << 24);
 }
 
+template <bool kWide>
 __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(const UgFusedParams P) {
+  using C = PairCfg<kWide>;
+  constexpr int kStages = C::kStages;
+  constexpr uint32_t kStageBytes = C::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t ring = (raw_addr + 1023u) & ~1023u;
@@ -98,8 +112,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs, ++iter) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
-        const int tile_n = task_tile_n(t);               // 256, or 128 for tail tiles: 128 / 64 columns per CTA
-        const int cta_cols = tile_n >> 1;
+        // Tile width 512 (wide kernel only), 256, or 128 for tail tiles.  A tile is 1 or 2 UMMA halves of up to 256
+        // columns; of each half this CTA loads its own 128 (64) columns.
+        const int tile_n = task_tile_n(t);
+        const int n_rem = min(tile_n, t.n - tc.nt * tile_n);
+        const int halves = (kWide && n_rem > 256) ? 2 : 1;
+        const int half_cols = min(tile_n, 256) >> 1;     // this CTA's columns per half
         trace_put(P, blockIdx.x, iter, UG_TR_TILE, static_cast<uint64_t>(tile) + 1u);
         trace_now(P, blockIdx.x, iter, UG_TR_PROD_BEGIN);
         uint64_t waited = 0;
@@ -112,7 +130,8 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
           }
           if (ok && sg.b_flag >= 0) {
             const int f = sg.b_flag + (tc.nt * tile_n) / UG_BN;
-            ok = flag_wait(flags + f, static_cast<uint32_t>(flag_need[f]), ctl);
+            for (int h = 0; ok && h < halves; ++h)         // a 512-column tile spans two staged chunks of 256
+              ok = flag_wait(flags + f + h, static_cast<uint32_t>(flag_need[f + h]), ctl);
           }
           if (!ok) break;
           if (w0 != 0) waited += global_timer_ns() - w0;
@@ -129,20 +148,23 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
           }
           const int nkb = (sg.k_len + UG_BK - 1) / UG_BK;
           const int ay = sg.a_row0 + tc.mt * 256 + static_cast<int>(rank) * 128;
-          const int bx = sg.b_col0 + tc.nt * tile_n + static_cast<int>(rank) * cta_cols;
-          const uint32_t cta_bytes = kPairABytes + (cta_cols > 64 ? 2u : 1u) * kBChunkBytes;
+          const int bx = sg.b_col0 + tc.nt * tile_n + static_cast<int>(rank) * half_cols;
+          const int chunks = half_cols > 64 ? 2 : 1;       // 64-column boxes per half
+          const uint32_t cta_bytes = kPairABytes + static_cast<uint32_t>(halves * chunks) * kBChunkBytes;
           for (int kb = 0; kb < nkb; ++kb) {
             ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, ctl);
             if (!ok) break;
             const uint32_t full_local = smem_u32(&sh->full[stage]);
             const uint32_t full_leader = mapa_shared(full_local, 0);
-            const uint32_t sa = ring + stage * kPairStageBytes;
+            const uint32_t sa = ring + stage * kStageBytes;
             const uint32_t sb = sa + kPairABytes;
             if (rank == 0) mbar_arrive_expect_tx(full_local, 2 * cta_bytes);
             tma_load_2d_pair(sa, amap, sg.a_col0 + kb * UG_BK, ay, full_leader);
-            tma_load_2d_pair(sb, bmap, bx, sg.b_row0 + kb * UG_BK, full_leader);
-            if (cta_cols > 64) tma_load_2d_pair(sb + kBChunkBytes, bmap, bx + 64, sg.b_row0 + kb * UG_BK, full_leader);
-            if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+            for (int h = 0; h < halves; ++h)
+              for (int c = 0; c < chunks; ++c)
+                tma_load_2d_pair(sb + h * kPairHalfBBytes + c * kBChunkBytes, bmap, bx + h * 256 + c * 64,
+                                 sg.b_row0 + kb * UG_BK, full_leader);
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
         }
         trace_put(P, blockIdx.x, iter, UG_TR_PROD_FLAGWAIT, waited);
@@ -158,33 +180,39 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs, ++iter) {
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
-        const uint32_t idesc = make_idesc_pair(static_cast<uint32_t>(task_tile_n(t)));
+        const int tile_n = task_tile_n(t);
+        const int halves = (kWide && min(tile_n, t.n - tc.nt * tile_n) > 256) ? 2 : 1;
+        const uint32_t idesc = make_idesc_pair(static_cast<uint32_t>(min(tile_n, 256)));
         ok = mbar_wait(smem_u32(&sh->acc_empty[acc]), acc_phase ^ 1u, ctl);
         if (!ok) break;
         tc_fence_after();
         trace_now(P, blockIdx.x, iter, UG_TR_MMA_BEGIN);
-        const uint32_t d_tmem = tmem_base + acc * UG_BN;
+        const uint32_t d_tmem = tmem_base + (C::kAccBufs == 2 ? acc * UG_BN : 0u);
         for (int kb = 0; kb < t.kblocks; ++kb) {
           ok = mbar_wait(smem_u32(&sh->full[stage]), phase, ctl);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t sa = ring + stage * kPairStageBytes;
+          const uint32_t sa = ring + stage * kStageBytes;
           const uint32_t sb = sa + kPairABytes;
 #pragma unroll
-          for (int ks = 0; ks < UG_BK / 16; ++ks)
-            umma_bf16_pair(d_tmem, make_desc_a(sa + ks * 32), make_desc_b(sb + ks * 2048), idesc,
-                           (kb > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < UG_BK / 16; ++ks) {
+            const uint64_t ad = make_desc_a(sa + ks * 32);
+            const uint32_t accum = (kb > 0 || ks > 0) ? 1u : 0u;
+            umma_bf16_pair(d_tmem, ad, make_desc_b(sb + ks * 2048), idesc, accum);
+            if (kWide && halves == 2)
+              umma_bf16_pair(d_tmem + UG_BN, ad, make_desc_b(sb + kPairHalfBBytes + ks * 2048), idesc, accum);
+          }
           const uint32_t e = smem_u32(&sh->empty[stage]);
           umma_commit_pair(mapa_shared(e, 0));
           umma_commit_pair(mapa_shared(e, 1));
-          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         const uint32_t f = smem_u32(&sh->acc_full[acc]);
         umma_commit_pair(mapa_shared(f, 0));
         umma_commit_pair(mapa_shared(f, 1));
         trace_now(P, blockIdx.x, iter, UG_TR_MMA_ISSUED);
-        acc ^= 1u;
+        if (C::kAccBufs == 2) acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
     }
@@ -205,44 +233,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       const int col0 = tc.nt * task_tile_n(t);
       const int n_rem = min(task_tile_n(t), t.n - col0);
       const int row0 = tc.mt * 256 + static_cast<int>(rank) * 128 + quad * 32;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * UG_BN;
-      if (row0 < t.m) {
-        for (int c = 0; c < n_rem; c += 32) {
-          if (t.c_dtype == 1 && task_c_vec(t) && n_rem - c >= 64) {
-            // bf16 output: two 32-column loads make one 128-byte row segment per row
-            uint32_t v0[32], v1[32];
-            tmem_ld_32x32(taddr + c, v0);
-            tmem_ld_32x32(taddr + c + 32, v1);
-            tmem_ld_wait();
-            const int r0w = row0;
-            store_chunk_bf16_64(epi_buf, v0, v1, lane,
-                                reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + static_cast<int64_t>(r0w) * t.ldc + col0 + c,
-                                t.ldc, min(32, t.m - r0w), t.c_mode);
-            c += 32;
-            continue;
-          }
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
-          const int ncols = min(32, n_rem - c);
-          if (task_c_vec(t) && ncols == 32) {
-            const int rows_valid = min(32, t.m - row0);
-            const int64_t off0 = static_cast<int64_t>(row0) * t.ldc + col0 + c;
-            if (t.c_dtype == 0)
-              store_chunk_f32(epi_buf, v, lane, reinterpret_cast<float*>(t.c_ptr) + off0, t.ldc, rows_valid, t.c_mode);
-            else
-              store_chunk_bf16(epi_buf, v, lane, reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + off0, t.ldc, rows_valid,
-                               t.c_mode);
-          } else {
-            store_chunk_scalar(epi_buf, v, lane, t.c_ptr, static_cast<int64_t>(row0) * t.ldc + col0 + c, t.ldc,
-                               min(32, t.m - row0), ncols, t.c_mode, t.c_dtype);
-          }
-        }
-      }
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + (C::kAccBufs == 2 ? acc * UG_BN : 0u);
+      if (row0 < t.m) epilogue_drain(taddr, t, row0, col0, n_rem, epi_buf, lane);
       if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
       tc_fence_before();
       mbar_arrive_cluster(mapa_shared(smem_u32(&sh->acc_empty[acc]), 0));
-      acc ^= 1u;
+      if (C::kAccBufs == 2) acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
   } else {
@@ -299,7 +295,10 @@ extern "C" int ug_fused_gemm_pair(const UgFusedParams* params, int grid, void* s
   if (e != cudaSuccess) return static_cast<int>(e);
   if (grid <= 0 || (grid & 1)) return static_cast<int>(cudaErrorInvalidValue);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    e = cudaFuncSetAttribute(ug_fused_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(ug_fused_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kPairSmemBytes));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaFuncSetAttribute(ug_fused_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(kPairSmemBytes));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
@@ -317,13 +316,15 @@ extern "C" int ug_fused_gemm_pair(const UgFusedParams* params, int grid, void* s
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, ug_fused_gemm_pair_kernel, *params);
+  // cta_pair == 2: tables were lowered for 256 x 512 tiles (single accumulator buffer, 4 stages of 48 KiB)
+  e = params->cta_pair == 2 ? cudaLaunchKernelEx(&cfg, ug_fused_gemm_pair_kernel<true>, *params)
+                            : cudaLaunchKernelEx(&cfg, ug_fused_gemm_pair_kernel<false>, *params);
   return static_cast<int>(e);
 }
 
 // Largest number of CTA pairs that can be resident at once on the current device (0 on error).
 extern "C" int ug_fused_gemm_pair_max_pairs(void) {
-  cudaError_t e = cudaFuncSetAttribute(ug_fused_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(ug_fused_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(kPairSmemBytes));
   if (e != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg;
@@ -339,6 +340,6 @@ extern "C" int ug_fused_gemm_pair_max_pairs(void) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  e = cudaOccupancyMaxActiveClusters(&n, ug_fused_gemm_pair_kernel, &cfg);
+  e = cudaOccupancyMaxActiveClusters(&n, ug_fused_gemm_pair_kernel<false>, &cfg);
   return e == cudaSuccess ? n : 0;
 }

@@ -163,9 +163,9 @@ class FusedProgramBuilder:
         self.range_check = range_check
         if tile_m is None and os.environ.get("UGEMM_TILE_M"):
             env = os.environ["UGEMM_TILE_M"]
-            tile_m = env if env == "pair" else int(env)
-        if tile_m not in (None, 128, 256, "pair"):
-            raise ValueError('tile_m must be 128, 256 or "pair"')
+            tile_m = env if env.startswith("pair") else int(env)
+        if tile_m not in (None, 128, 256, "pair", "pair512"):
+            raise ValueError('tile_m must be 128, 256, "pair" or "pair512"')
         self.tile_m = tile_m
         self.tasks: list[TaskSpec] = []
 
@@ -216,11 +216,18 @@ class FusedProgramBuilder:
     def build(self, status_ptr: int) -> FusedProgram:
         dev = self.device
         variant = self.choose_tile_m()
-        pair = variant == "pair"            # two CTAs share a 256 x 256 tile; each loads 128 rows of A
+        pair = variant in ("pair", "pair512")   # two CTAs share a 256-row tile; each loads 128 rows of A
+        wide = variant == "pair512"             # ... of 512 columns (two UMMAs per K step, accumulators fill TMEM)
         BM = 256 if pair else variant
         a_box_rows = 128 if pair else BM
         workers = (self.num_sms // 2) if pair else self.num_sms
-        tasks = self._split_tail(self.tasks, BM, workers) if os.environ.get("UGEMM_TAIL_SPLIT", "1") != "0" else self.tasks
+        tasks = self.tasks
+        if wide:
+            from dataclasses import replace
+
+            tasks = [replace(t, tile_n=2 * BN) if t.tile_n == BN else t for t in tasks]
+        if os.environ.get("UGEMM_TAIL_SPLIT", "1") != "0":
+            tasks = self._split_tail(tasks, BM, workers, 2 * BN if wide else BN)
         map_keys: dict[tuple, int] = {}
         map_specs: list[tuple] = []
 
@@ -355,7 +362,10 @@ class FusedProgramBuilder:
                         if s >= tr["seg_count"]:
                             continue
                         sa, sb = seg_sources[tr["seg_begin"] + s]
-                        for st, ci in ((sa, mt), (sb, nt * tr["tile_n"] // BN)):
+                        b_first = nt * tr["tile_n"] // BN            # a 512-column tile spans two staged chunks
+                        b_last = min(((nt + 1) * tr["tile_n"] - 1) // BN, (sb.num_chunks - 1) if sb else 0)
+                        wanted = [(sa, mt)] + [(sb, ci) for ci in range(b_first, b_last + 1)]
+                        for st, ci in wanted:
                             if st is None:
                                 continue
                             key = (id(st), ci)
@@ -414,11 +424,11 @@ class FusedProgramBuilder:
         params.num_flags = num_flags
         params.total_tiles = total_tiles
         params.tile_m = BM
-        params.cta_pair = 1 if pair else 0
+        params.cta_pair = 2 if wide else (1 if pair else 0)
         params.prefetch_kblocks = int(os.environ.get("UGEMM_PREFETCH_KBLOCKS", _PREFETCH_KBLOCKS))
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
-                     pieces=len(ordered), staged_bytes=staging_bytes, tile_m="pair" if pair else BM,
+                     pieces=len(ordered), staged_bytes=staging_bytes, tile_m=variant if pair else BM,
                      remote_bytes=sum(st.src.rows * st.src.cols * st.src.elem_bytes for st in staged.values()
                                       if st.src.remote), grid=grid)
         return FusedProgram(device=dev, tables=tables, staging=staging, params=params, grid=grid,
@@ -426,12 +436,14 @@ class FusedProgramBuilder:
                             stats=stats)
 
     @staticmethod
-    def _split_tail(tasks: list[TaskSpec], bm: int, workers: int) -> list[TaskSpec]:
+    def _split_tail(tasks: list[TaskSpec], bm: int, workers: int, tn: int = BN) -> list[TaskSpec]:
         """Halve the tile width of the tiles that would form the last, partly filled wave.
 
-        With T tiles on W workers the last wave holds T mod W tiles; if they are at most W / 2 and consist of whole
-        trailing tile columns of the last task(s), those columns become a task of their own with 128-column tiles:
-        twice as many tiles of half the cost, so the last wave costs half a tile time instead of a full one."""
+        With T tiles (``tn`` columns wide) on W workers the last wave holds T mod W tiles; if they are at most W / 2
+        and consist of whole trailing tile columns of the last task(s), those columns become a task of their own with
+        tiles of ``tn / 2`` columns: twice as many tiles of half the cost, so the last wave costs half a tile time
+        instead of a full one."""
+        BN = tn                                                        # noqa: N806 (tile width of this variant)
         counts = [((t.m + bm - 1) // bm) * ((t.n + BN - 1) // BN) for t in tasks]
         total = sum(counts)
         tail = total % workers if workers > 0 else 0
@@ -447,14 +459,15 @@ class FusedProgramBuilder:
             if m_tiles > 2048 // bm:          # several raster bands: the last tiles are not whole columns
                 return list(tasks)
             if m_tiles * n_tiles <= remaining:
-                out[idx] = FusedProgramBuilder._columns(t, 0, t.n, 128)
+                out[idx] = FusedProgramBuilder._columns(t, 0, t.n, BN // 2)
                 remaining -= m_tiles * n_tiles
                 idx -= 1
                 continue
             if remaining % m_tiles:
                 return list(tasks)
             cut = (n_tiles - remaining // m_tiles) * BN
-            out[idx:idx + 1] = [FusedProgramBuilder._columns(t, 0, cut, BN), FusedProgramBuilder._columns(t, cut, t.n, 128)]
+            out[idx:idx + 1] = [FusedProgramBuilder._columns(t, 0, cut, BN),
+                                FusedProgramBuilder._columns(t, cut, t.n, BN // 2)]
             remaining = 0
         return out
 
