@@ -12,16 +12,17 @@ namespace ugfused {
 
 using namespace ugptx;
 
-constexpr int kNumThreads = 448;      // 14 warps: producer, UMMA, 4 epilogue, 8 fetch
+constexpr int kNumThreads = 448;      // 14 warps: producer, UMMA, 8 epilogue, 4 fetch
 constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
-constexpr int kFetchWarp0 = 6;  // warps 2..5 are the epilogue, 6..13 fetch
+constexpr int kEpiWarp0 = 2;    // warps 2..9 are the epilogue: two per TMEM lane quadrant (warp & 3), the first
+constexpr int kNumEpiWarps = 8; // four drain the left part of a tile's columns, the other four the right part
+constexpr int kFetchWarp0 = 10; // warps 10..13 fetch
 
 constexpr uint32_t kBChunkBytes = UG_BK * 64 * 2;      // 8 KiB: 64 k rows x 64 n elements
 constexpr uint32_t kBBytes = 4 * kBChunkBytes;         // 32 KiB
-constexpr uint32_t kEpiRowFloats = 36;                 // 32 columns + 4 of padding: conflict-free v4 rows
-constexpr uint32_t kEpiWarpBytes = 32 * kEpiRowFloats * 4;
-constexpr uint32_t kEpiBytes = 4 * kEpiWarpBytes;      // one transpose buffer per epilogue warp
+constexpr uint32_t kEpiWarpBytes = 32 * 128;           // 32 rows of 128 bytes, 16-byte groups XOR-swizzled by row
+constexpr uint32_t kEpiBytes = kNumEpiWarps * kEpiWarpBytes;   // one transpose buffer per epilogue warp
 constexpr uint32_t kTmemCols = 512;                    // 128 lanes x 512 fp32 columns: all of TMEM
 
 struct WaitCtl {
@@ -159,6 +160,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Word offset of 16-byte group `group` (0..7) of row `row` in a transpose buffer.  Rows are 128 bytes without
+// padding; XOR-ing the group with the row number keeps both phases free of bank conflicts: lanes of a quarter warp
+// write the same group of 8 different rows, and read 8 different groups of one row.
+__device__ __forceinline__ int epi_off(int row, int group) { return row * 32 + ((group ^ (row & 7)) << 2); }
+
 // Full, 16-byte aligned chunks: the warp's 32 x 32 block of accumulators goes through a
 // shared-memory buffer so that each store / reduction instruction covers whole 128-byte row
 // segments (4 rows of fp32, 8 rows of bf16) instead of 32 different rows.  This matters most for
@@ -167,14 +173,14 @@ __device__ __forceinline__ void store_chunk_f32(float* sb, const uint32_t (&v)[3
                                                 int64_t ldc, int rows_valid, int mode) {
 #pragma unroll
   for (int j = 0; j < 8; ++j)
-    *reinterpret_cast<uint4*>(sb + lane * kEpiRowFloats + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    *reinterpret_cast<uint4*>(sb + epi_off(lane, j)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
   __syncwarp();
   const int rsub = lane >> 3, cseg = (lane & 7) * 4;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int r = i * 4 + rsub;
     if (r < rows_valid) {
-      float4 x = *reinterpret_cast<const float4*>(sb + r * kEpiRowFloats + cseg);
+      float4 x = *reinterpret_cast<const float4*>(sb + epi_off(r, lane & 7));
       float4* g = reinterpret_cast<float4*>(c_base + r * ldc + cseg);
       if (mode == 1) {
         red_add_v4_f32(g, x.x, x.y, x.z, x.w);
@@ -236,7 +242,7 @@ __device__ __forceinline__ void store_chunk_bf16(float* sbf, const uint32_t (&v)
 __device__ __forceinline__ void store_chunk_bf16_64(float* sbf, const uint32_t (&v0)[32], const uint32_t (&v1)[32],
                                                     int lane, __nv_bfloat16* c_base, int64_t ldc, int rows_valid,
                                                     int mode) {
-  unsigned char* sb = reinterpret_cast<unsigned char*>(sbf);          // row pitch 144 bytes (36 words)
+  // rows of 128 payload bytes, swizzled like the fp32 rows
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     uint4 q;
@@ -244,12 +250,12 @@ __device__ __forceinline__ void store_chunk_bf16_64(float* sbf, const uint32_t (
     q.y = pack_bf16x2(__uint_as_float(v0[8 * j + 2]), __uint_as_float(v0[8 * j + 3]));
     q.z = pack_bf16x2(__uint_as_float(v0[8 * j + 4]), __uint_as_float(v0[8 * j + 5]));
     q.w = pack_bf16x2(__uint_as_float(v0[8 * j + 6]), __uint_as_float(v0[8 * j + 7]));
-    *reinterpret_cast<uint4*>(sb + lane * 144 + j * 16) = q;
+    *reinterpret_cast<uint4*>(sbf + epi_off(lane, j)) = q;
     q.x = pack_bf16x2(__uint_as_float(v1[8 * j + 0]), __uint_as_float(v1[8 * j + 1]));
     q.y = pack_bf16x2(__uint_as_float(v1[8 * j + 2]), __uint_as_float(v1[8 * j + 3]));
     q.z = pack_bf16x2(__uint_as_float(v1[8 * j + 4]), __uint_as_float(v1[8 * j + 5]));
     q.w = pack_bf16x2(__uint_as_float(v1[8 * j + 6]), __uint_as_float(v1[8 * j + 7]));
-    *reinterpret_cast<uint4*>(sb + lane * 144 + 64 + j * 16) = q;
+    *reinterpret_cast<uint4*>(sbf + epi_off(lane, j + 4)) = q;
   }
   __syncwarp();
   const int rsub = lane >> 3, seg = lane & 7;
@@ -257,7 +263,7 @@ __device__ __forceinline__ void store_chunk_bf16_64(float* sbf, const uint32_t (
   for (int i = 0; i < 8; ++i) {
     const int r = i * 4 + rsub;
     if (r < rows_valid) {
-      uint4 x = *reinterpret_cast<const uint4*>(sb + r * 144 + seg * 16);
+      uint4 x = *reinterpret_cast<const uint4*>(sbf + epi_off(r, seg));
       uint4* g = reinterpret_cast<uint4*>(c_base + r * ldc + seg * 8);
       if (mode == 1) {
         red_add_v4_bf16x2(g, x.x, x.y, x.z, x.w);
@@ -287,11 +293,11 @@ __device__ __forceinline__ void store_chunk_scalar(float* sb, const uint32_t (&v
                                                    int dtype) {
 #pragma unroll
   for (int j = 0; j < 8; ++j)
-    *reinterpret_cast<uint4*>(sb + lane * kEpiRowFloats + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    *reinterpret_cast<uint4*>(sb + epi_off(lane, j)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
   __syncwarp();
   if (lane < ncols) {
     for (int r = 0; r < rows_valid; ++r) {
-      const float x = sb[r * kEpiRowFloats + lane];
+      const float x = sb[epi_off(r, lane >> 2) + (lane & 3)];
       const int64_t off = elem_off + r * ldc + lane;
       if (dtype == 0) {
         float* g = reinterpret_cast<float*>(c_ptr) + off;

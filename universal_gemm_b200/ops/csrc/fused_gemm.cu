@@ -9,10 +9,12 @@
 //   warp 1      UMMA issuer: tcgen05.mma 128x256x16 bf16 -> fp32 accumulators in
 //               TMEM (two 256-column buffers, so the epilogue of tile i overlaps
 //               the main loop of tile i+1); owns TMEM allocation.
-//   warps 2-5   epilogue: tcgen05.ld -> registers -> C.  C may live in a peer's
-//               memory; then the partial tile is pushed with red.global.add
-//               (the remote accumulate of Stationary-B and of replica reduction).
-//   warps 6-13  fetch warps: copy remote (peer memory, plain P2P loads) or
+//   warps 2-9   epilogue: tcgen05.ld -> registers -> shared-memory transpose -> C, two
+//               warps per TMEM lane quadrant, each draining half of the tile's columns.
+//               C may live in a peer's memory; then the partial tile is stored or
+//               pushed with red.global.add (the remote accumulate of Stationary-B
+//               and of replica reduction).
+//   warps 10-13 fetch warps: copy remote (peer memory, plain P2P loads) or
 //               misaligned operand slices into a local staging buffer, piece by
 //               piece, and bump a per-chunk counter; the producer of whichever
 //               CTA needs the chunk waits on that counter before its TMA loads.
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&sh->acc_full[b]), 1);
-      mbar_init(smem_u32(&sh->acc_empty[b]), 128);
+      mbar_init(smem_u32(&sh->acc_empty[b]), kNumEpiWarps * 32);
     }
     sh->abort = 0;
     fence_mbar_init();
@@ -152,13 +154,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
           const int nkb = (sg.k_len + UG_BK - 1) / UG_BK;
           const int ay = sg.a_row0 + tc.mt * BM;
           const int bx = sg.b_col0 + tc.nt * tile_n;
+          // L2 prefetch by designated tiles only: of the tiles of a wave that share an A row block (or a B column
+          // panel) one asks L2 for the K blocks ahead, so that the lock-step demand loads of all of them hit.
+          const bool pf_a = P.prefetch_kblocks > 0 && (tc.nt & 7) == 0;
+          const bool pf_b = P.prefetch_kblocks > 0 && tc.mt % max(t.group_m, 1) == 0;
           for (int kb = 0; kb < nkb; ++kb) {
-            // Pull the operands of a later K block into L2 now: all CTAs walk K in step, so the first
-            // toucher of a line would otherwise pay the DRAM latency inside the smem ring's short cover.
-            if (P.prefetch_kblocks > 0 && kb + P.prefetch_kblocks < nkb) {
+            if ((pf_a || pf_b) && kb + P.prefetch_kblocks < nkb) {
               const int pk = (kb + P.prefetch_kblocks) * UG_BK;
-              tma_prefetch_l2_2d(amap, sg.a_col0 + pk, ay);
-              for (int c = 0; c < n_chunks; ++c) tma_prefetch_l2_2d(bmap, bx + c * 64, sg.b_row0 + pk);
+              if (pf_a) tma_prefetch_l2_2d(amap, sg.a_col0 + pk, ay);
+              if (pf_b)
+                for (int c = 0; c < n_chunks; ++c) tma_prefetch_l2_2d(bmap, bx + c * 64, sg.b_row0 + pk);
             }
             ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, ctl);
             if (!ok) break;
@@ -219,8 +224,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     }
   } else if (warp < kFetchWarp0) {
     // ------------------------------------------------------------ epilogue
-    const int quad = warp & 3;   // TMEM lane quadrant this warp may read
-    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + quad * (kEpiWarpBytes / 4);
+    const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int part = (warp - kEpiWarp0) >> 2;        // 0: left part of the tile's columns, 1: right part
+    const bool tracer = warp == kEpiWarp0 && lane == 0;
+    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + (warp - kEpiWarp0) * (kEpiWarpBytes / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     int iter = 0;
@@ -230,17 +237,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
       if (!ok) break;
       tc_fence_after();
-      if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
+      if (tracer) trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
       const int col0 = tc.nt * task_tile_n(t);
       const int n_rem = min(task_tile_n(t), t.n - col0);
+      // the two warps of a quadrant split the columns on a multiple of 64 (whole 128-byte row segments each)
+      const int split = min(n_rem, ((n_rem + 127) >> 7) << 6);
+      const int c0 = part == 0 ? 0 : split, cn = part == 0 ? split : n_rem - split;
 #pragma unroll
       for (int h = 0; h < C::kHalves; ++h) {
-        if (tc.mt * BM + h * 128 >= t.m) break;       // whole half outside the region (warp-uniform)
+        if (cn <= 0 || tc.mt * BM + h * 128 >= t.m) break;     // nothing to do (warp-uniform)
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                (C::kAccBufs == 2 ? acc * UG_BN : static_cast<uint32_t>(h) * UG_BN);
-        epilogue_drain(taddr, t, tc.mt * BM + h * 128 + quad * 32, col0, n_rem, epi_buf, lane);
+        epilogue_drain(taddr + c0, t, tc.mt * BM + h * 128 + quad * 32, col0 + c0, cn, epi_buf, lane);
       }
-      if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
+      if (tracer) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->acc_empty[acc]));
       if (C::kAccBufs == 2) acc ^= 1u;

@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&sh->acc_full[b]), 1);
-      mbar_init(smem_u32(&sh->acc_empty[b]), 256);
+      mbar_init(smem_u32(&sh->acc_empty[b]), 2 * kNumEpiWarps * 32);
     }
     sh->abort = 0;
     fence_mbar_init();
@@ -151,7 +151,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
           const int bx = sg.b_col0 + tc.nt * tile_n + static_cast<int>(rank) * half_cols;
           const int chunks = half_cols > 64 ? 2 : 1;       // 64-column boxes per half
           const uint32_t cta_bytes = kPairABytes + static_cast<uint32_t>(halves * chunks) * kBChunkBytes;
+          // L2 prefetch by designated tiles only: of the tiles of a wave that share an A row block (or a B column
+          // panel) one asks L2 for the K blocks ahead, so that the lock-step demand loads of all of them hit.
+          const bool pf_a = P.prefetch_kblocks > 0 && (tc.nt & 7) == 0;
+          const bool pf_b = P.prefetch_kblocks > 0 && tc.mt % max(t.group_m, 1) == 0;
           for (int kb = 0; kb < nkb; ++kb) {
+            if ((pf_a || pf_b) && kb + P.prefetch_kblocks < nkb) {
+              const int pk = (kb + P.prefetch_kblocks) * UG_BK;
+              if (pf_a) tma_prefetch_l2_2d(amap, sg.a_col0 + pk, ay);
+              if (pf_b)
+                for (int h = 0; h < halves; ++h)
+                  for (int c = 0; c < chunks; ++c) tma_prefetch_l2_2d(bmap, bx + h * 256 + c * 64, sg.b_row0 + pk);
+            }
             ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, ctl);
             if (!ok) break;
             const uint32_t full_local = smem_u32(&sh->full[stage]);
@@ -218,8 +229,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     }
   } else if (warp < kFetchWarp0) {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
-    const int quad = warp & 3;
-    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + quad * (kEpiWarpBytes / 4);
+    const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int part = (warp - kEpiWarp0) >> 2;        // 0: left part of the tile's columns, 1: right part
+    const bool tracer = warp == kEpiWarp0 && lane == 0;
+    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + (warp - kEpiWarp0) * (kEpiWarpBytes / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     int iter = 0;
@@ -229,13 +242,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
       if (!ok) break;
       tc_fence_after();
-      if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
+      if (tracer) trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
       const int col0 = tc.nt * task_tile_n(t);
       const int n_rem = min(task_tile_n(t), t.n - col0);
       const int row0 = tc.mt * 256 + static_cast<int>(rank) * 128 + quad * 32;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + (C::kAccBufs == 2 ? acc * UG_BN : 0u);
-      if (row0 < t.m) epilogue_drain(taddr, t, row0, col0, n_rem, epi_buf, lane);
-      if (quad == 2 && lane == 0) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
+      // the two warps of a quadrant split the columns on a multiple of 64 (whole 128-byte row segments each)
+      const int split = min(n_rem, ((n_rem + 127) >> 7) << 6);
+      const int c0 = part == 0 ? 0 : split, cn = part == 0 ? split : n_rem - split;
+      if (row0 < t.m && cn > 0) epilogue_drain(taddr + c0, t, row0, col0 + c0, cn, epi_buf, lane);
+      if (tracer) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
       tc_fence_before();
       mbar_arrive_cluster(mapa_shared(smem_u32(&sh->acc_empty[acc]), 0));
       if (C::kAccBufs == 2) acc ^= 1u;
