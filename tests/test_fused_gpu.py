@@ -346,6 +346,7 @@ def test_kernel_timeline_records_every_tile(tile_m):
     s = TR.summarize(arr, pair=pair)
     assert s["recorded_tiles"] == prog.stats["tiles"] and s["pieces_copied"] == prog.num_pieces
     assert 0 < s["main_us_mean"] < s["kernel_us"] < 1e5
+    assert 0.1 < s["sm_clock_ghz"] < 3.0               # SM cycles per globaltimer nanosecond
     assert TR.to_chrome_trace(arr)
     prog.disable_trace()
     run_program(prog, _dev())

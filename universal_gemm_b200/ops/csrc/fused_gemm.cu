@@ -99,7 +99,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     }
     sh->abort = 0;
     fence_mbar_init();
-    if (uint64_t* ts = trace_summary(P, blockIdx.x)) ts[UG_TR_S_START] = global_timer_ns();
+    if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
+      ts[UG_TR_S_START] = global_timer_ns();
+      ts[UG_TR_S_CLK_START] = static_cast<uint64_t>(clock64());
+    }
   }
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&sh->tmem_base), kTmemCols);
@@ -154,17 +157,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
           const int nkb = (sg.k_len + UG_BK - 1) / UG_BK;
           const int ay = sg.a_row0 + tc.mt * BM;
           const int bx = sg.b_col0 + tc.nt * tile_n;
-          // L2 prefetch by designated tiles only: of the tiles of a wave that share an A row block (or a B column
-          // panel) one asks L2 for the K blocks ahead, so that the lock-step demand loads of all of them hit.
-          const bool pf_a = P.prefetch_kblocks > 0 && (tc.nt & 7) == 0;
-          const bool pf_b = P.prefetch_kblocks > 0 && tc.mt % max(t.group_m, 1) == 0;
           for (int kb = 0; kb < nkb; ++kb) {
-            if ((pf_a || pf_b) && kb + P.prefetch_kblocks < nkb) {
-              const int pk = (kb + P.prefetch_kblocks) * UG_BK;
-              if (pf_a) tma_prefetch_l2_2d(amap, sg.a_col0 + pk, ay);
-              if (pf_b)
-                for (int c = 0; c < n_chunks; ++c) tma_prefetch_l2_2d(bmap, bx + c * 64, sg.b_row0 + pk);
-            }
             ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, ctl);
             if (!ok) break;
             const uint32_t fb = smem_u32(&sh->full[stage]);
@@ -297,7 +290,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
   tc_fence_after();
   if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
   if (threadIdx.x == 0) {
-    if (uint64_t* ts = trace_summary(P, blockIdx.x)) ts[UG_TR_S_END] = global_timer_ns();
+    if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
+      ts[UG_TR_S_END] = global_timer_ns();
+      ts[UG_TR_S_CLK_END] = static_cast<uint64_t>(clock64());
+    }
   }
 }
 

@@ -33,8 +33,13 @@ constexpr uint32_t kPairSmemBytes = kPairRingBytes + 1024 + 256 + kEpiBytes;
 
 template <bool kWide>
 struct PairCfg {
-  static constexpr int kStages = kWide ? 4 : 6;
-  static constexpr uint32_t kStageBytes = kPairABytes + (kWide ? 2u : 1u) * kPairHalfBBytes;   // 48 / 32 KiB
+  // A stage holds kKps K blocks (sub-stages); one full / empty barrier round trip and one pair of commits per stage.
+  // The 256-column tile takes two K blocks per stage: with one, the per-stage work of the issuing thread (barrier
+  // wait, fence, four UMMAs, two commits) took longer than the 512 tensor cycles the stage feeds.
+  static constexpr int kKps = kWide ? 1 : 2;
+  static constexpr uint32_t kSubBytes = kPairABytes + (kWide ? 2u : 1u) * kPairHalfBBytes;   // 48 / 32 KiB per K block
+  static constexpr uint32_t kStageBytes = kKps * kSubBytes;                                   // 48 / 64 KiB
+  static constexpr int kStages = kWide ? 4 : 3;
   static constexpr int kAccBufs = kWide ? 1 : 2;
   static_assert(kStages * kStageBytes == kPairRingBytes, "ring size");
 };
@@ -57,7 +62,9 @@ template <bool kWide>
 __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(const UgFusedParams P) {
   using C = PairCfg<kWide>;
   constexpr int kStages = C::kStages;
+  constexpr int kKps = C::kKps;
   constexpr uint32_t kStageBytes = C::kStageBytes;
+  constexpr uint32_t kSubBytes = C::kSubBytes;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t ring = (raw_addr + 1023u) & ~1023u;
@@ -90,7 +97,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     }
     sh->abort = 0;
     fence_mbar_init();
-    if (uint64_t* ts = trace_summary(P, blockIdx.x)) ts[UG_TR_S_START] = global_timer_ns();
+    if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
+      ts[UG_TR_S_START] = global_timer_ns();
+      ts[UG_TR_S_CLK_START] = static_cast<uint64_t>(clock64());
+    }
   }
   if (warp == kMmaWarp) {
     tmem_alloc_pair(smem_u32(&sh->tmem_base), kTmemCols);
@@ -151,30 +161,23 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
           const int bx = sg.b_col0 + tc.nt * tile_n + static_cast<int>(rank) * half_cols;
           const int chunks = half_cols > 64 ? 2 : 1;       // 64-column boxes per half
           const uint32_t cta_bytes = kPairABytes + static_cast<uint32_t>(halves * chunks) * kBChunkBytes;
-          // L2 prefetch by designated tiles only: of the tiles of a wave that share an A row block (or a B column
-          // panel) one asks L2 for the K blocks ahead, so that the lock-step demand loads of all of them hit.
-          const bool pf_a = P.prefetch_kblocks > 0 && (tc.nt & 7) == 0;
-          const bool pf_b = P.prefetch_kblocks > 0 && tc.mt % max(t.group_m, 1) == 0;
-          for (int kb = 0; kb < nkb; ++kb) {
-            if ((pf_a || pf_b) && kb + P.prefetch_kblocks < nkb) {
-              const int pk = (kb + P.prefetch_kblocks) * UG_BK;
-              if (pf_a) tma_prefetch_l2_2d(amap, sg.a_col0 + pk, ay);
-              if (pf_b)
-                for (int h = 0; h < halves; ++h)
-                  for (int c = 0; c < chunks; ++c) tma_prefetch_l2_2d(bmap, bx + h * 256 + c * 64, sg.b_row0 + pk);
-            }
+          for (int kb = 0; kb < nkb; kb += kKps) {
+            const int cnt = min(kKps, nkb - kb);           // K blocks in this stage
             ok = mbar_wait(smem_u32(&sh->empty[stage]), phase ^ 1u, ctl);
             if (!ok) break;
             const uint32_t full_local = smem_u32(&sh->full[stage]);
             const uint32_t full_leader = mapa_shared(full_local, 0);
-            const uint32_t sa = ring + stage * kStageBytes;
-            const uint32_t sb = sa + kPairABytes;
-            if (rank == 0) mbar_arrive_expect_tx(full_local, 2 * cta_bytes);
-            tma_load_2d_pair(sa, amap, sg.a_col0 + kb * UG_BK, ay, full_leader);
-            for (int h = 0; h < halves; ++h)
-              for (int c = 0; c < chunks; ++c)
-                tma_load_2d_pair(sb + h * kPairHalfBBytes + c * kBChunkBytes, bmap, bx + h * 256 + c * 64,
-                                 sg.b_row0 + kb * UG_BK, full_leader);
+            if (rank == 0) mbar_arrive_expect_tx(full_local, 2 * cta_bytes * static_cast<uint32_t>(cnt));
+            for (int sub = 0; sub < cnt; ++sub) {
+              const uint32_t sa = ring + stage * kStageBytes + sub * kSubBytes;
+              const uint32_t sb = sa + kPairABytes;
+              const int kx = (kb + sub) * UG_BK;
+              tma_load_2d_pair(sa, amap, sg.a_col0 + kx, ay, full_leader);
+              for (int h = 0; h < halves; ++h)
+                for (int c = 0; c < chunks; ++c)
+                  tma_load_2d_pair(sb + h * kPairHalfBBytes + c * kBChunkBytes, bmap, bx + h * 256 + c * 64,
+                                   sg.b_row0 + kx, full_leader);
+            }
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
         }
@@ -199,24 +202,32 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
         tc_fence_after();
         trace_now(P, blockIdx.x, iter, UG_TR_MMA_BEGIN);
         const uint32_t d_tmem = tmem_base + (C::kAccBufs == 2 ? acc * UG_BN : 0u);
-        for (int kb = 0; kb < t.kblocks; ++kb) {
-          ok = mbar_wait(smem_u32(&sh->full[stage]), phase, ctl);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t sa = ring + stage * kStageBytes;
-          const uint32_t sb = sa + kPairABytes;
+        bool first = true;                                 // the first UMMA of a tile overwrites the accumulator
+        for (int sgi = 0; ok && sgi < t.seg_count; ++sgi) {
+          const int nkb = (segs[t.seg_begin + sgi].k_len + UG_BK - 1) / UG_BK;
+          for (int kb = 0; kb < nkb; kb += kKps) {
+            const int cnt = min(kKps, nkb - kb);
+            ok = mbar_wait(smem_u32(&sh->full[stage]), phase, ctl);
+            if (!ok) break;
+            tc_fence_after();
+            for (int sub = 0; sub < cnt; ++sub) {
+              const uint32_t sa = ring + stage * kStageBytes + sub * kSubBytes;
+              const uint32_t sb = sa + kPairABytes;
 #pragma unroll
-          for (int ks = 0; ks < UG_BK / 16; ++ks) {
-            const uint64_t ad = make_desc_a(sa + ks * 32);
-            const uint32_t accum = (kb > 0 || ks > 0) ? 1u : 0u;
-            umma_bf16_pair(d_tmem, ad, make_desc_b(sb + ks * 2048), idesc, accum);
-            if (kWide && halves == 2)
-              umma_bf16_pair(d_tmem + UG_BN, ad, make_desc_b(sb + kPairHalfBBytes + ks * 2048), idesc, accum);
+              for (int ks = 0; ks < UG_BK / 16; ++ks) {
+                const uint64_t ad = make_desc_a(sa + ks * 32);
+                const uint32_t accum = first ? 0u : 1u;
+                first = false;
+                umma_bf16_pair(d_tmem, ad, make_desc_b(sb + ks * 2048), idesc, accum);
+                if (kWide && halves == 2)
+                  umma_bf16_pair(d_tmem + UG_BN, ad, make_desc_b(sb + kPairHalfBBytes + ks * 2048), idesc, accum);
+              }
+            }
+            const uint32_t e = smem_u32(&sh->empty[stage]);
+            umma_commit_pair(mapa_shared(e, 0));
+            umma_commit_pair(mapa_shared(e, 1));
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
-          const uint32_t e = smem_u32(&sh->empty[stage]);
-          umma_commit_pair(mapa_shared(e, 0));
-          umma_commit_pair(mapa_shared(e, 1));
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         const uint32_t f = smem_u32(&sh->acc_full[acc]);
@@ -298,7 +309,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
   tc_fence_after();
   if (warp == kMmaWarp) tmem_dealloc_pair(tmem_base, kTmemCols);
   if (threadIdx.x == 0) {
-    if (uint64_t* ts = trace_summary(P, blockIdx.x)) ts[UG_TR_S_END] = global_timer_ns();
+    if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
+      ts[UG_TR_S_END] = global_timer_ns();
+      ts[UG_TR_S_CLK_END] = static_cast<uint64_t>(clock64());
+    }
   }
 }
 

@@ -82,7 +82,7 @@ typedef struct {
   int32_t total_tiles;
   int32_t tile_m;         // rows per output tile: 128 (0 means 128) or 256
   uint64_t timeout_ns;    // limit of every in-kernel wait
-  int32_t prefetch_kblocks;  // L2 prefetch distance of the TMA producer in K blocks (0 = off)
+  int32_t prefetch_kblocks;  // unused (L2 prefetch by the TMA producer measured slower at every distance); keep 0
   int32_t cta_pair;          // 1: tables were lowered for the CTA-pair kernel (ug_fused_gemm_pair)
   uint64_t trace;            // 0 = off; else uint64[grid][trace_slots + 1][8] timeline records (see UG_TR_*)
   int32_t trace_slots;       // tile iterations recorded per CTA (later ones are dropped)
@@ -100,7 +100,8 @@ enum {
   UG_TR_MMA_ISSUED = 5,  // last UMMA of the tile issued
   UG_TR_EPI_BEGIN = 6,   // accumulator complete (seen by the first epilogue warp)
   UG_TR_EPI_END = 7,     // first epilogue warp finished its rows
-  UG_TR_S_START = 0, UG_TR_S_FETCH_END = 1, UG_TR_S_END = 2, UG_TR_S_PIECES = 3
+  UG_TR_S_START = 0, UG_TR_S_FETCH_END = 1, UG_TR_S_END = 2, UG_TR_S_PIECES = 3,
+  UG_TR_S_CLK_START = 4, UG_TR_S_CLK_END = 5   // clock64() of the SM at start / end: SM clock = cycles / nanoseconds
 };
 
 // ----------------------------------------------------------------------------

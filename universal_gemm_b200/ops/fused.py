@@ -27,12 +27,17 @@ from . import native
 from .native import BN, BK
 
 _PIECE_BYTES = 32 * 1024
-_EFF_128 = 0.66          # measured tensor-pipe share of the 128-row main loop
-_EFF_256 = 0.83          # ... of the one-CTA 256-row main loop
-_EFF_PAIR = 0.80         # ... of the CTA-pair main loop
-_LINK_BYTES_PER_CYCLE = 300.0    # ~570 GB/s of red.add into a peer at ~1.9 GHz
-_HBM_BYTES_PER_CYCLE = 8000.0    # epilogue stores mostly land in L2
-_PREFETCH_KBLOCKS = 0     # L2 prefetch distance of the TMA producer (K blocks)
+# Tile variants.  kb_us: microseconds per 64-deep K block of one tile; epi_us: epilogue of a full fp32 tile stored
+# into local memory; both measured with the in-kernel timeline on an 8192^3 GEMM under the power cap.  "hidden": the
+# accumulators are double buffered, so the epilogue runs behind the next tile's main loop.
+_VARIANTS = {
+    128: dict(rows=128, cols=256, pair=False, kb_us=0.483, epi_us=3.6, hidden=True),
+    256: dict(rows=256, cols=256, pair=False, kb_us=0.696, epi_us=7.1, hidden=False),
+    "pair": dict(rows=256, cols=256, pair=True, kb_us=0.394, epi_us=4.0, hidden=True),
+    "pair512": dict(rows=256, cols=512, pair=True, kb_us=0.695, epi_us=6.7, hidden=False),
+}
+_AUTO_VARIANTS = (128, 256, "pair")      # "pair512" measured level with 256 and quantises worse: on request only
+_REMOTE_EPILOGUE_FACTOR = 2.0            # stores / red.add into a peer's C against local stores
 
 
 def _round_up(x: int, m: int) -> int:
@@ -180,31 +185,35 @@ class FusedProgramBuilder:
 
     # ------------------------------------------------------------------ tile shape
     def choose_tile_m(self):
-        """Pick the tile variant (128, 256 or "pair") from a cycle model of the persistent grid.
+        """Pick the tile variant (128, 256 or "pair") from a time model of the persistent grid.
 
-        Per tile: main loop = K blocks x 512 tensor cycles per 128 rows / measured tensor-pipe share of the
-        variant; epilogue = C bytes of the tile over HBM, or over this CTA's share of the NVLink when C is a
-        peer's memory.  The 128-row tile and the CTA-pair tile hide the epilogue behind the next main loop
-        (cost max(main, epilogue)); the one-CTA 256-row tile fills TMEM and pays main + epilogue."""
+        Per tile: main loop = K blocks x the variant's measured time per K block; epilogue = the variant's measured
+        epilogue time, scaled by the bytes of C it moves (bf16 halves them, read-modify-write doubles them) and by a
+        factor when C is a peer's memory.  Variants with double-buffered accumulators pay max(main, epilogue) per
+        tile, the others main + epilogue.  Tiles are dealt round-robin to the workers (CTAs, or CTA pairs) as the
+        kernel does; the variant with the smallest busiest worker wins."""
         if self.tile_m is not None:
             return self.tile_m
-        sms = self.num_sms
         best = None
-        for variant, rows, eff, hidden, workers in ((128, 128, _EFF_128, True, sms), (256, 256, _EFF_256, False, sms),
-                                                    ("pair", 256, _EFF_PAIR, True, sms // 2)):
+        for variant in _AUTO_VARIANTS:
+            v = _VARIANTS[variant]
+            workers = self.num_sms // 2 if v["pair"] else self.num_sms
             if workers < 1:
                 continue
             per_worker = [0.0] * workers
             tile = 0
             for t in self.tasks:
                 kblocks = sum((a.cols + BK - 1) // BK for a, _ in t.segments)
-                tiles = ((t.m + rows - 1) // rows) * ((t.n + BN - 1) // BN)
-                sm_rows = 128 if variant == "pair" else rows           # rows one SM multiplies per tile
-                main = kblocks * (sm_rows // 128) * 512.0 / eff
-                c_bytes = sm_rows * BN * (4 if t.c_dtype == native.DT_F32 else 2) * (2 if t.c_mode == native.C_ADD else 1)
-                epi = 1500.0 + c_bytes / (_LINK_BYTES_PER_CYCLE / sms if t.c_remote else _HBM_BYTES_PER_CYCLE / sms)
-                cost = max(main, epi) if hidden else main + epi
-                for _ in range(tiles):
+                tiles = ((t.m + v["rows"] - 1) // v["rows"]) * ((t.n + v["cols"] - 1) // v["cols"])
+                main = kblocks * v["kb_us"]
+                epi = v["epi_us"] * (0.75 if t.c_dtype == native.DT_BF16 else 1.0) \
+                    * (1.5 if t.c_mode == native.C_ADD else 1.0) * (_REMOTE_EPILOGUE_FACTOR if t.c_remote else 1.0)
+                cost = max(main, epi) if v["hidden"] else main + epi
+                full, rest = divmod(tiles, workers)
+                if full:
+                    for w in range(workers):
+                        per_worker[w] += full * cost
+                for _ in range(rest):
                     per_worker[tile % workers] += cost
                     tile += 1
             total = max(per_worker)
@@ -425,7 +434,7 @@ class FusedProgramBuilder:
         params.total_tiles = total_tiles
         params.tile_m = BM
         params.cta_pair = 2 if wide else (1 if pair else 0)
-        params.prefetch_kblocks = int(os.environ.get("UGEMM_PREFETCH_KBLOCKS", _PREFETCH_KBLOCKS))
+        params.prefetch_kblocks = 0
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
                      pieces=len(ordered), staged_bytes=staging_bytes, tile_m=variant if pair else BM,

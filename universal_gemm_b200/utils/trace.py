@@ -23,7 +23,7 @@ from typing import Any
 import numpy as np
 
 TILE, PROD_BEGIN, PROD_FLAGWAIT, PROD_END, MMA_BEGIN, MMA_ISSUED, EPI_BEGIN, EPI_END = range(8)
-S_START, S_FETCH_END, S_END, S_PIECES = range(4)
+S_START, S_FETCH_END, S_END, S_PIECES, S_CLK_START, S_CLK_END = range(6)
 
 enabled: bool = os.environ.get("UGEMM_TRACE", "0") not in ("", "0")
 
@@ -94,6 +94,10 @@ def summarize(arr: np.ndarray, *, pair: bool = False) -> dict:
                  "recorded_tiles": int(rec[::2].sum() if pair else rec.sum()),
                  "kernel_us": us(t_end - t0),
                  "cta_start_spread_us": us(int(starts[live].max()) - t0)}
+    clk = (summ[:, S_CLK_END] - summ[:, S_CLK_START])[live]
+    dur = (summ[:, S_END] - summ[:, S_START])[live]
+    if (clk > 0).any() and (dur > 0).all():
+        out["sm_clock_ghz"] = float(np.median(clk[clk > 0] / dur[clk > 0]))      # SM cycles per nanosecond
     has_mma = rec & (tiles[:, :, MMA_BEGIN] > 0) & (tiles[:, :, EPI_BEGIN] > 0)
     if has_mma.any():
         main = (tiles[:, :, EPI_BEGIN] - tiles[:, :, MMA_BEGIN])[has_mma]
