@@ -40,7 +40,7 @@ __device__ __forceinline__ void raise_error(const WaitCtl& ctl, uint32_t code) {
 // single threads with plain stores; the host reads it after the kernel.  Costs one uniform branch when off.
 __device__ __forceinline__ uint64_t* trace_slot(const UgFusedParams& P, int cta, int iter) {
   if (P.trace == 0 || iter > P.trace_slots) return nullptr;
-  return reinterpret_cast<uint64_t*>(P.trace) + (static_cast<int64_t>(cta) * (P.trace_slots + 1) + iter) * 8;
+  return reinterpret_cast<uint64_t*>(P.trace) + (static_cast<int64_t>(cta) * (P.trace_slots + 1) + iter) * UG_TR_FIELDS;
 }
 __device__ __forceinline__ void trace_put(const UgFusedParams& P, int cta, int iter, int field, uint64_t v) {
   if (P.trace == 0 || iter >= P.trace_slots) return;
@@ -55,10 +55,44 @@ __device__ __forceinline__ uint64_t* trace_summary(const UgFusedParams& P, int c
   return P.trace == 0 ? nullptr : trace_slot(P, cta, P.trace_slots);
 }
 
+// Tile hand-off inside a CTA when tiles are claimed dynamically (UgFusedParams::sched): the TMA producer claims the
+// tile of iteration i and publishes (i + 1) << 32 | tile in slot i % 16 with one 64-bit store; the UMMA issuer and
+// the epilogue warps read it from there.  No role is ever 16 tiles ahead of another (the operand ring and the two
+// accumulator buffers bound the lead), so a slot is not overwritten before everyone has read it.
+constexpr int kTileQueueSlots = 16;
+struct TileQueue {
+  volatile unsigned long long slot[kTileQueueSlots];
+};
+__device__ __forceinline__ unsigned long long tileq_word(int iter, int tile) {
+  return (static_cast<unsigned long long>(iter + 1) << 32) | static_cast<uint32_t>(tile);
+}
+__device__ __forceinline__ void tileq_publish(TileQueue* q, int iter, int tile) {
+  q->slot[iter & (kTileQueueSlots - 1)] = tileq_word(iter, tile);
+}
+// Bounded wait for the tile of iteration `iter`; -1 after an abort or a timeout.
+__device__ __forceinline__ int tileq_get(const TileQueue* q, int iter, const WaitCtl& ctl);
+
 // Bounded mbarrier wait.  Returns false after an abort or a timeout.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtl& ctl) {
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xffu) == 0u) {
+      if (*ctl.abort) return false;
+      if (global_timer_ns() > ctl.deadline) {
+        raise_error(ctl, UG_ERR_TIMEOUT_MBAR);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// The same wait with a pause between polls, for roles that wait a whole main loop (the epilogue warps): fewer
+// issue slots and less power spent on polling, at the price of up to `sleep_ns` of wake-up latency.
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity, const WaitCtl& ctl, uint32_t sleep_ns) {
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if (sleep_ns != 0u) __nanosleep(sleep_ns);
     if ((++spins & 0xffu) == 0u) {
       if (*ctl.abort) return false;
       if (global_timer_ns() > ctl.deadline) {
@@ -84,6 +118,23 @@ __device__ __forceinline__ bool flag_wait(const uint32_t* counter, uint32_t need
     }
   }
   return true;
+}
+
+__device__ __forceinline__ int tileq_get(const TileQueue* q, int iter, const WaitCtl& ctl) {
+  const unsigned long long want = static_cast<unsigned long long>(iter + 1);
+  uint32_t spins = 0;
+  for (;;) {
+    const unsigned long long w = q->slot[iter & (kTileQueueSlots - 1)];
+    if ((w >> 32) == want) return static_cast<int>(static_cast<uint32_t>(w));
+    if ((++spins & 0x3fu) == 0u) {
+      if (*ctl.abort) return -1;
+      if (global_timer_ns() > ctl.deadline) {
+        raise_error(ctl, UG_ERR_TIMEOUT_MBAR);
+        return -1;
+      }
+      __nanosleep(32);
+    }
+  }
 }
 
 // Columns per output tile of a task: UG_BN, or a narrower width stored in the upper half of c_vec

@@ -61,6 +61,7 @@ struct Shared {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile uint32_t abort;
+  TileQueue tq;
 };
 
 template <int BM>
@@ -87,6 +88,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
   ctl.abort = &sh->abort;
   ctl.status = reinterpret_cast<uint32_t*>(P.status);
   ctl.deadline = global_timer_ns() + P.timeout_ns;
+  // Static schedule: CTA b runs tiles b, b + grid, ...  Dynamic: after its first tile the producer claims the next
+  // unclaimed tile from a global counter and hands it to the other roles through sh->tq.
+  const bool dyn = P.sched != 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -98,6 +102,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       mbar_init(smem_u32(&sh->acc_empty[b]), kNumEpiWarps * 32);
     }
     sh->abort = 0;
+    for (int i = 0; i < kTileQueueSlots; ++i) sh->tq.slot[i] = 0ull;
     fence_mbar_init();
     if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
       ts[UG_TR_S_START] = global_timer_ns();
@@ -119,8 +124,12 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       uint32_t stage = 0, phase = 0;
       uint64_t seen[4] = {0, 0, 0, 0};   // tensor maps already acquired by this thread
       bool ok = true;
-      int iter = 0;
-      for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x, ++iter) {
+      int tile = blockIdx.x;
+      for (int iter = 0; ok; ++iter) {
+        if (iter > 0) tile = dyn ? static_cast<int>(gridDim.x + atomicAdd(reinterpret_cast<uint32_t*>(P.sched), 1u))
+                                 : tile + static_cast<int>(gridDim.x);
+        if (dyn) tileq_publish(&sh->tq, iter, tile);
+        if (tile >= P.total_tiles) break;
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
         const int tile_n = task_tile_n(t);
@@ -179,8 +188,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      int iter = 0;
-      for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x, ++iter) {
+      for (int iter = 0; ok; ++iter) {
+        const int tile = dyn ? tileq_get(&sh->tq, iter, ctl) : static_cast<int>(blockIdx.x + iter * gridDim.x);
+        if (tile < 0 || tile >= P.total_tiles) break;
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
         const int n_rem = min(task_tile_n(t), t.n - tc.nt * task_tile_n(t));
@@ -189,6 +199,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
         if (!ok) break;
         tc_fence_after();
         trace_now(P, blockIdx.x, iter, UG_TR_MMA_BEGIN);
+        trace_put(P, blockIdx.x, iter, UG_TR_MMA_CLK, static_cast<uint64_t>(clock64()));
         const uint32_t d_tmem = tmem_base + (C::kAccBufs == 2 ? acc * UG_BN : 0u);
         for (int kb = 0; kb < t.kblocks; ++kb) {
           ok = mbar_wait(smem_u32(&sh->full[stage]), phase, ctl);
@@ -223,14 +234,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + (warp - kEpiWarp0) * (kEpiWarpBytes / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    int iter = 0;
-    for (int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x, ++iter) {
+    for (int iter = 0; ok; ++iter) {
+      const int tile = dyn ? tileq_get(&sh->tq, iter, ctl) : static_cast<int>(blockIdx.x + iter * gridDim.x);
+      if (tile < 0 || tile >= P.total_tiles) break;
       const TileCoord tc = locate(tasks, P.num_tasks, tile);
       const UgTask& t = tasks[tc.task];
-      ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
+      ok = mbar_wait_backoff(smem_u32(&sh->acc_full[acc]), acc_phase, ctl, static_cast<uint32_t>(P.epi_poll_ns));
       if (!ok) break;
       tc_fence_after();
-      if (tracer) trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
+      if (tracer) {
+        trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
+        trace_put(P, blockIdx.x, iter, UG_TR_EPI_CLK, static_cast<uint64_t>(clock64()));
+      }
       const int col0 = tc.nt * task_tile_n(t);
       const int n_rem = min(task_tile_n(t), t.n - col0);
       // the two warps of a quadrant split the columns on a multiple of 64 (whole 128-byte row segments each)
@@ -289,6 +304,15 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
   __syncthreads();
   tc_fence_after();
   if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && dyn) {
+    // Every role of this CTA is done, so it claims no more tiles: the last CTA to get here re-arms the counters.
+    uint32_t* sched = reinterpret_cast<uint32_t*>(P.sched);
+    if (atomicAdd(sched + 1, 1u) == gridDim.x - 1) {
+      sched[0] = 0u;
+      sched[1] = 0u;
+      __threadfence();
+    }
+  }
   if (threadIdx.x == 0) {
     if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
       ts[UG_TR_S_END] = global_timer_ns();

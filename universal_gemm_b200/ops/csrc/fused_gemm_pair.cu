@@ -51,6 +51,7 @@ struct PairShared {
   uint64_t acc_empty[2];          // used in rank 0: both CTAs' epilogues drained the buffer
   uint32_t tmem_base;
   volatile uint32_t abort;
+  TileQueue tq;                   // per CTA; the leader's producer writes both CTAs' queues
 };
 
 // Instruction descriptor of the pair UMMA: M = 256 (128 per CTA), N = n (256, or 128 for tail tiles).
@@ -85,6 +86,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
   ctl.abort = &sh->abort;
   ctl.status = reinterpret_cast<uint32_t*>(P.status);
   ctl.deadline = global_timer_ns() + P.timeout_ns;
+  // Static schedule: pair p runs tiles p, p + pairs, ...  Dynamic: after its first tile the leader CTA's producer
+  // claims the next unclaimed tile from a global counter and writes it into the tile queues of both CTAs.
+  const bool dyn = P.sched != 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
@@ -96,6 +100,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       mbar_init(smem_u32(&sh->acc_empty[b]), 2 * kNumEpiWarps * 32);
     }
     sh->abort = 0;
+    for (int i = 0; i < kTileQueueSlots; ++i) sh->tq.slot[i] = 0ull;
     fence_mbar_init();
     if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
       ts[UG_TR_S_START] = global_timer_ns();
@@ -118,8 +123,20 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       uint32_t stage = 0, phase = 0;
       uint64_t seen[4] = {0, 0, 0, 0};
       bool ok = true;
-      int iter = 0;
-      for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs, ++iter) {
+      int tile = pair_id;
+      for (int iter = 0; ok; ++iter) {
+        if (!dyn) {
+          if (iter > 0) tile += num_pairs;
+        } else if (rank == 0) {
+          if (iter > 0) tile = num_pairs + static_cast<int>(atomicAdd(reinterpret_cast<uint32_t*>(P.sched), 1u));
+          const uint32_t slot = smem_u32(const_cast<unsigned long long*>(&sh->tq.slot[iter & (kTileQueueSlots - 1)]));
+          st_shared_cluster_u64(mapa_shared(slot, 1), tileq_word(iter, tile));   // the other CTA's queue
+          tileq_publish(&sh->tq, iter, tile);
+        } else {
+          tile = tileq_get(&sh->tq, iter, ctl);
+          if (tile < 0) break;
+        }
+        if (tile >= P.total_tiles) break;
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
         // Tile width 512 (wide kernel only), 256, or 128 for tail tiles.  A tile is 1 or 2 UMMA halves of up to 256
@@ -190,8 +207,9 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     if (lane == 0 && rank == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      int iter = 0;
-      for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs, ++iter) {
+      for (int iter = 0; ok; ++iter) {
+        const int tile = dyn ? tileq_get(&sh->tq, iter, ctl) : pair_id + iter * num_pairs;
+        if (tile < 0 || tile >= P.total_tiles) break;
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
         const int tile_n = task_tile_n(t);
@@ -201,6 +219,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
         if (!ok) break;
         tc_fence_after();
         trace_now(P, blockIdx.x, iter, UG_TR_MMA_BEGIN);
+        trace_put(P, blockIdx.x, iter, UG_TR_MMA_CLK, static_cast<uint64_t>(clock64()));
         const uint32_t d_tmem = tmem_base + (C::kAccBufs == 2 ? acc * UG_BN : 0u);
         bool first = true;                                 // the first UMMA of a tile overwrites the accumulator
         for (int sgi = 0; ok && sgi < t.seg_count; ++sgi) {
@@ -246,14 +265,18 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + (warp - kEpiWarp0) * (kEpiWarpBytes / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    int iter = 0;
-    for (int tile = pair_id; ok && tile < P.total_tiles; tile += num_pairs, ++iter) {
+    for (int iter = 0; ok; ++iter) {
+      const int tile = dyn ? tileq_get(&sh->tq, iter, ctl) : pair_id + iter * num_pairs;
+      if (tile < 0 || tile >= P.total_tiles) break;
       const TileCoord tc = locate(tasks, P.num_tasks, tile);
       const UgTask& t = tasks[tc.task];
-      ok = mbar_wait(smem_u32(&sh->acc_full[acc]), acc_phase, ctl);
+      ok = mbar_wait_backoff(smem_u32(&sh->acc_full[acc]), acc_phase, ctl, static_cast<uint32_t>(P.epi_poll_ns));
       if (!ok) break;
       tc_fence_after();
-      if (tracer) trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
+      if (tracer) {
+        trace_now(P, blockIdx.x, iter, UG_TR_EPI_BEGIN);
+        trace_put(P, blockIdx.x, iter, UG_TR_EPI_CLK, static_cast<uint64_t>(clock64()));
+      }
       const int col0 = tc.nt * task_tile_n(t);
       const int n_rem = min(task_tile_n(t), t.n - col0);
       const int row0 = tc.mt * 256 + static_cast<int>(rank) * 128 + quad * 32;
@@ -308,6 +331,16 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
   cluster_sync_all();              // neither CTA leaves while the other may still touch its shared memory
   tc_fence_after();
   if (warp == kMmaWarp) tmem_dealloc_pair(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && dyn && rank == 0) {
+    // Both CTAs of this pair are done (cluster barrier above), so the pair claims no more tiles: the last pair to
+    // get here re-arms the counters for the next launch.
+    uint32_t* sched = reinterpret_cast<uint32_t*>(P.sched);
+    if (atomicAdd(sched + 1, 1u) == static_cast<uint32_t>(num_pairs - 1)) {
+      sched[0] = 0u;
+      sched[1] = 0u;
+      __threadfence();
+    }
+  }
   if (threadIdx.x == 0) {
     if (uint64_t* ts = trace_summary(P, blockIdx.x)) {
       ts[UG_TR_S_END] = global_timer_ns();

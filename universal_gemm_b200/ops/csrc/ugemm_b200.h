@@ -84,9 +84,11 @@ typedef struct {
   uint64_t timeout_ns;    // limit of every in-kernel wait
   int32_t prefetch_kblocks;  // unused (L2 prefetch by the TMA producer measured slower at every distance); keep 0
   int32_t cta_pair;          // 1: tables were lowered for the CTA-pair kernel (ug_fused_gemm_pair)
-  uint64_t trace;            // 0 = off; else uint64[grid][trace_slots + 1][8] timeline records (see UG_TR_*)
+  uint64_t trace;            // 0 = off; else uint64[grid][trace_slots + 1][UG_TR_FIELDS] timeline records (see UG_TR_*)
   int32_t trace_slots;       // tile iterations recorded per CTA (later ones are dropped)
-  int32_t reserved;
+  int32_t epi_poll_ns;       // pause between the epilogue warps' polls of the accumulator barrier (0 = none)
+  uint64_t sched;            // 0 = static round-robin tiles; else uint32[2] {next tile claim, finished workers}, both
+                             // zero at launch (the last worker to finish resets them): workers claim tiles dynamically
 } UgFusedParams;
 
 // Fields of one timeline record (globaltimer nanoseconds unless noted).  Record `trace_slots` of a CTA is
@@ -100,6 +102,9 @@ enum {
   UG_TR_MMA_ISSUED = 5,  // last UMMA of the tile issued
   UG_TR_EPI_BEGIN = 6,   // accumulator complete (seen by the first epilogue warp)
   UG_TR_EPI_END = 7,     // first epilogue warp finished its rows
+  UG_TR_MMA_CLK = 8,     // clock64() of the SM at UG_TR_MMA_BEGIN
+  UG_TR_EPI_CLK = 9,     // clock64() of the SM at UG_TR_EPI_BEGIN: (EPI_CLK - MMA_CLK) / (EPI_BEGIN - MMA_BEGIN) = SM clock
+  UG_TR_FIELDS = 16,     // uint64 words per record
   UG_TR_S_START = 0, UG_TR_S_FETCH_END = 1, UG_TR_S_END = 2, UG_TR_S_PIECES = 3,
   UG_TR_S_CLK_START = 4, UG_TR_S_CLK_END = 5   // clock64() of the SM at start / end: SM clock = cycles / nanoseconds
 };

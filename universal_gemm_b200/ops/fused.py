@@ -115,13 +115,13 @@ class FusedProgram:
 
     # ------------------------------------------------------------------ optional per-tile timeline
     def enable_trace(self, slots: int | None = None) -> None:
-        """Make later launches record a timeline: one 8 x uint64 record per (CTA, tile iteration) plus a
+        """Make later launches record a timeline: one record of ``native.TRACE_FIELDS`` uint64 words per (CTA, tile iteration) plus a
         summary record per CTA (layout: ``UG_TR_*`` in ugemm_b200.h).  Each launch overwrites the previous one."""
         workers = max(self.grid // 2 if self.params.cta_pair else self.grid, 1)
-        if slots is None:
-            slots = (int(self.params.total_tiles) + workers - 1) // workers
+        if slots is None:     # with dynamic claiming a fast worker runs more tiles than the average
+            slots = (int(self.params.total_tiles) + workers - 1) // workers * 5 // 4 + 2
         slots = max(int(slots), 1)
-        self._trace = torch.zeros(self.grid, slots + 1, 8, dtype=torch.int64, device=self.device)
+        self._trace = torch.zeros(self.grid, slots + 1, native.TRACE_FIELDS, dtype=torch.int64, device=self.device)
         self.params.trace = self._trace.data_ptr()
         self.params.trace_slots = slots
 
@@ -131,7 +131,7 @@ class FusedProgram:
         self.params.trace_slots = 0
 
     def read_trace(self):
-        """The timeline of the last launch as a numpy array ``[grid, slots + 1, 8]`` (synchronises the device);
+        """The timeline of the last launch as a numpy array ``[grid, slots + 1, native.TRACE_FIELDS]`` (synchronises the device);
         ``None`` when tracing is off."""
         if self._trace is None:
             return None
@@ -410,7 +410,7 @@ class FusedProgramBuilder:
             return b + bytes((-len(b)) % align)
 
         sections = [pad(bytes(maps_blob)), pad(task_arr.tobytes()), pad(seg_arr.tobytes()), pad(piece_arr.tobytes()),
-                    pad(flag_need.tobytes()), pad(bytes(4 * (num_flags + 1)))]
+                    pad(flag_need.tobytes()), pad(bytes(4 * (num_flags + 1))), pad(bytes(8))]
         offsets = np.cumsum([0] + [len(s) for s in sections])
         blob = np.frombuffer(b"".join(sections), dtype=np.uint8).copy()
         tables = torch.empty(len(blob) + 256, dtype=torch.uint8, device=dev)
@@ -435,6 +435,9 @@ class FusedProgramBuilder:
         params.tile_m = BM
         params.cta_pair = 2 if wide else (1 if pair else 0)
         params.prefetch_kblocks = 0
+        # Dynamic tile claiming (two uint32 counters, re-armed by the kernel itself) unless switched off.
+        params.sched = base + int(offsets[6]) if os.environ.get("UGEMM_DYNAMIC_TILES", "0") != "0" else 0
+        params.epi_poll_ns = int(os.environ.get("UGEMM_EPI_POLL_NS", "0"))
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
                      pieces=len(ordered), staged_bytes=staging_bytes, tile_m=variant if pair else BM,

@@ -81,15 +81,19 @@ class FusedParams(ctypes.Structure):
         ("total_tiles", c_int32), ("tile_m", c_int32),
         ("timeout_ns", c_uint64),
         ("prefetch_kblocks", c_int32), ("cta_pair", c_int32),
-        ("trace", c_uint64), ("trace_slots", c_int32), ("reserved", c_int32),
+        ("trace", c_uint64), ("trace_slots", c_int32), ("epi_poll_ns", c_int32),
+        ("sched", c_uint64),
     ]
+
+
+TRACE_FIELDS = 16     # uint64 words per timeline record (UG_TR_FIELDS)
 
 
 def check_layouts() -> None:
     assert SEGMENT_DTYPE.itemsize == 64, SEGMENT_DTYPE.itemsize
     assert TASK_DTYPE.itemsize == 64, TASK_DTYPE.itemsize
     assert PIECE_DTYPE.itemsize == 48, PIECE_DTYPE.itemsize
-    assert ctypes.sizeof(FusedParams) == 120, ctypes.sizeof(FusedParams)
+    assert ctypes.sizeof(FusedParams) == 128, ctypes.sizeof(FusedParams)
 
 
 check_layouts()

@@ -22,7 +22,7 @@ from typing import Any
 
 import numpy as np
 
-TILE, PROD_BEGIN, PROD_FLAGWAIT, PROD_END, MMA_BEGIN, MMA_ISSUED, EPI_BEGIN, EPI_END = range(8)
+TILE, PROD_BEGIN, PROD_FLAGWAIT, PROD_END, MMA_BEGIN, MMA_ISSUED, EPI_BEGIN, EPI_END, MMA_CLK, EPI_CLK = range(10)
 S_START, S_FETCH_END, S_END, S_PIECES, S_CLK_START, S_CLK_END = range(6)
 
 enabled: bool = os.environ.get("UGEMM_TRACE", "0") not in ("", "0")
@@ -77,7 +77,7 @@ def detach_all() -> None:
 
 # ----------------------------------------------------------------------------- analysis (numpy only)
 def summarize(arr: np.ndarray, *, pair: bool = False) -> dict:
-    """Figures of one launch from its ``[grid, slots + 1, 8]`` timeline (times in microseconds from the first
+    """Figures of one launch from its ``[grid, slots + 1, fields]`` timeline (times in microseconds from the first
     CTA's start)."""
     arr = np.asarray(arr, dtype=np.int64)
     grid, slots = arr.shape[0], arr.shape[1] - 1
@@ -111,6 +111,17 @@ def summarize(arr: np.ndarray, *, pair: bool = False) -> dict:
             if sel.any():
                 by_iter.append(round(us((tiles[:, i, EPI_BEGIN] - tiles[:, i, MMA_BEGIN])[sel].mean()), 2))
         out["main_us_by_iteration"] = by_iter
+        if arr.shape[2] > EPI_CLK:
+            # SM clock during each main loop: cycles between the two stamps over nanoseconds between them
+            cyc = tiles[:, :, EPI_CLK] - tiles[:, :, MMA_CLK]
+            ns = tiles[:, :, EPI_BEGIN] - tiles[:, :, MMA_BEGIN]
+            okc = has_mma & (tiles[:, :, MMA_CLK] > 0) & (cyc > 0) & (ns > 0)
+            by_iter = []
+            for i in range(slots):
+                sel = okc[:, i]
+                if sel.any():
+                    by_iter.append(round(float((cyc[:, i][sel] / ns[:, i][sel]).mean()), 3))
+            out["sm_clock_ghz_by_iteration"] = by_iter
     has_epi = rec & (tiles[:, :, EPI_BEGIN] > 0) & (tiles[:, :, EPI_END] > 0)
     if has_epi.any():
         epi = (tiles[:, :, EPI_END] - tiles[:, :, EPI_BEGIN])[has_epi]
