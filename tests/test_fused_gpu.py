@@ -351,3 +351,25 @@ def test_kernel_timeline_records_every_tile(tile_m):
     prog.disable_trace()
     run_program(prog, _dev())
     _status_ok()
+
+
+@pytest.mark.parametrize("tile_m", [128, 256, "pair", "pair512"])
+def test_dynamic_tile_claiming_many_tiles_per_worker(tile_m, monkeypatch):
+    """Dynamic tile claiming with more than 16 tiles per worker (the in-CTA tile queue wraps around), launched
+    several times in a row (the kernel re-arms its claim counters itself)."""
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.gemm import build_gemm_program, run_program
+
+    monkeypatch.setenv("UGEMM_DYNAMIC_TILES", "1")
+    torch.manual_seed(5)
+    m, n, k = 8192, 24576, 128
+    a = torch.randn(m, k, device=_dev()).bfloat16()
+    b = (torch.randn(k, n, device=_dev()) / k ** 0.5).bfloat16()
+    c = torch.zeros(m, n, device=_dev())
+    prog = build_gemm_program([a], [b], c, mode=native.C_STORE, tile_m=tile_m)
+    workers = prog.grid // 2 if str(tile_m).startswith("pair") else prog.grid
+    assert prog.params.sched != 0 and prog.stats["tiles"] > 16 * workers
+    for _ in range(3):
+        run_program(prog, _dev())
+    _status_ok()
+    torch.testing.assert_close(c, a.float() @ b.float(), rtol=2e-3, atol=2e-3)

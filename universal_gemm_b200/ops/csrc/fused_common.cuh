@@ -23,6 +23,7 @@ constexpr uint32_t kBChunkBytes = UG_BK * 64 * 2;      // 8 KiB: 64 k rows x 64 
 constexpr uint32_t kBBytes = 4 * kBChunkBytes;         // 32 KiB
 constexpr uint32_t kEpiWarpBytes = 32 * 128;           // 32 rows of 128 bytes, 16-byte groups XOR-swizzled by row
 constexpr uint32_t kEpiBytes = kNumEpiWarps * kEpiWarpBytes;   // one transpose buffer per epilogue warp
+constexpr uint32_t kCtlBytes = 512;                    // barriers, flags and the tile queue; the epilogue buffers follow
 constexpr uint32_t kTmemCols = 512;                    // 128 lanes x 512 fp32 columns: all of TMEM
 
 struct WaitCtl {

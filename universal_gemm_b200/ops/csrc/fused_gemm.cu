@@ -51,7 +51,7 @@ struct Cfg {
   static constexpr uint32_t kABytes = BM * UG_BK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kRingBytes = kStages * kStageBytes;
-  static constexpr uint32_t kSmemBytes = kRingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kEpiBytes;
+  static constexpr uint32_t kSmemBytes = kRingBytes + 1024 /*alignment slack*/ + kCtlBytes + kEpiBytes;
 };
 
 struct Shared {
@@ -63,6 +63,7 @@ struct Shared {
   volatile uint32_t abort;
   TileQueue tq;
 };
+static_assert(sizeof(Shared) <= kCtlBytes, "control block overlaps the epilogue buffers");
 
 template <int BM>
 __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgFusedParams P) {
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
     const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
     const int part = (warp - kEpiWarp0) >> 2;        // 0: left part of the tile's columns, 1: right part
     const bool tracer = warp == kEpiWarp0 && lane == 0;
-    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + (warp - kEpiWarp0) * (kEpiWarpBytes / 4);
+    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + kCtlBytes) + (warp - kEpiWarp0) * (kEpiWarpBytes / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (int iter = 0; ok; ++iter) {

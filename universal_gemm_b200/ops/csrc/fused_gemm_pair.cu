@@ -29,7 +29,7 @@ constexpr int kPairStages = 6;                                  // most stages o
 constexpr uint32_t kPairABytes = 128 * UG_BK * 2;               // 16 KiB: this CTA's 128 rows of A
 constexpr uint32_t kPairHalfBBytes = 2 * kBChunkBytes;          // 16 KiB: this CTA's 128 columns of one 256-column UMMA
 constexpr uint32_t kPairRingBytes = 6 * (kPairABytes + kPairHalfBBytes);   // 192 KiB = 4 x 48 KiB as well
-constexpr uint32_t kPairSmemBytes = kPairRingBytes + 1024 + 256 + kEpiBytes;
+constexpr uint32_t kPairSmemBytes = kPairRingBytes + 1024 + kCtlBytes + kEpiBytes;
 
 template <bool kWide>
 struct PairCfg {
@@ -53,6 +53,7 @@ struct PairShared {
   volatile uint32_t abort;
   TileQueue tq;                   // per CTA; the leader's producer writes both CTAs' queues
 };
+static_assert(sizeof(PairShared) <= kCtlBytes, "control block overlaps the epilogue buffers");
 
 // Instruction descriptor of the pair UMMA: M = 256 (128 per CTA), N = n (256, or 128 for tail tiles).
 __device__ __forceinline__ uint32_t make_idesc_pair(uint32_t n) {
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
     const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
     const int part = (warp - kEpiWarp0) >> 2;        // 0: left part of the tile's columns, 1: right part
     const bool tracer = warp == kEpiWarp0 && lane == 0;
-    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + 256) + (warp - kEpiWarp0) * (kEpiWarpBytes / 4);
+    float* epi_buf = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sh) + kCtlBytes) + (warp - kEpiWarp0) * (kEpiWarpBytes / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (int iter = 0; ok; ++iter) {

@@ -435,8 +435,13 @@ class FusedProgramBuilder:
         params.tile_m = BM
         params.cta_pair = 2 if wide else (1 if pair else 0)
         params.prefetch_kblocks = 0
-        # Dynamic tile claiming (two uint32 counters, re-armed by the kernel itself) unless switched off.
-        params.sched = base + int(offsets[6]) if os.environ.get("UGEMM_DYNAMIC_TILES", "0") != "0" else 0
+        # Dynamic tile claiming (two uint32 counters, re-armed by the kernel itself).  Default: on for the CTA-pair
+        # variants, where it measured +6-9 % on the headline GEMM (workers finish 90 us apart instead of 450 us); off
+        # for the one-CTA variants, where it measured level: under the power cap the SMs that finish early leave their
+        # share of the power budget to the others.  UGEMM_DYNAMIC_TILES=0 / 1 overrides.
+        dyn_env = os.environ.get("UGEMM_DYNAMIC_TILES", "")
+        dynamic = pair if dyn_env == "" else dyn_env != "0"
+        params.sched = base + int(offsets[6]) if dynamic else 0
         params.epi_poll_ns = int(os.environ.get("UGEMM_EPI_POLL_NS", "0"))
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
