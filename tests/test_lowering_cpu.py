@@ -79,3 +79,29 @@ def test_operand_alignment_rules():
     assert not OperandSlice(base=4096, ld=100, row0=0, col0=0, rows=1, cols=8).tma_ok()        # pitch not 16 B
     assert not OperandSlice(base=4096, ld=128, row0=0, col0=0, rows=1, cols=8, remote=True).tma_ok()
     assert OperandSlice(base=4096, ld=128, row0=0, col0=0, rows=1, cols=8, remote=True).vector_ok()
+
+
+def test_tail_split_of_wide_pair_tiles():
+    """256 x 512 tiles: 82 tiles on 74 pairs leave 8 tail tiles = 4 trailing tile columns of 2 tile rows, re-cut to 256."""
+    from dataclasses import replace
+
+    tasks = [replace(_task(512, 41 * 512, 128), tile_n=512)]
+    out = FusedProgramBuilder._split_tail(tasks, 256, 74, 512)
+    assert [t.tile_n for t in out] == [512, 256]
+    assert out[0].n == 37 * 512 and out[1].n == 4 * 512 and out[1].c_ptr == out[0].c_ptr + out[0].n * 4
+    tiles = sum(((t.m + 255) // 256) * ((t.n + t.tile_n - 1) // t.tile_n) for t in out)
+    assert tiles == 74 + 16
+
+
+def test_tile_variant_model_long_k_prefers_the_256_row_tile_locally():
+    """Local C, long K: the exposed epilogue of the 256-row tile costs less than the pair tile's slower main loop;
+    with few K blocks per tile the hidden epilogue wins."""
+    long_k = FusedProgramBuilder("cpu", num_sms=148)
+    long_k.add_task(_task(8192, 49152, 12288))
+    assert long_k.choose_tile_m() == 256
+    short_k = FusedProgramBuilder("cpu", num_sms=148)
+    short_k.add_task(_task(8192, 8192, 1024))
+    assert short_k.choose_tile_m() == "pair"
+    explicit = FusedProgramBuilder("cpu", num_sms=148, tile_m="pair512")
+    explicit.add_task(_task(300, 200, 157))
+    assert explicit.choose_tile_m() == "pair512"
