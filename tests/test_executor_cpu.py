@@ -172,3 +172,25 @@ def test_redistribute_and_ring_matmul_cpu():
                                rtol=1e-4, atol=1e-4)
     with pytest.raises(ValueError):
         ug.row_partitioned_matmul(halves[0], mats[0][1], mats[0][2])
+
+
+def test_guard_regions_detect_writes_outside_an_allocation():
+    """With guard regions on, a full plan leaves them intact; a write past the end of a shard is reported."""
+    full_a, full_b, full_c = make_inputs(37, 29, 41, seed=11)
+    cluster = ug.EmulatedCluster(4, "cpu", guard_bytes=512)
+    mats = build_cluster_matrices(cluster, full_a, full_b, full_c, ("block", "row", "column"), 1, torch.float32,
+                                  torch.float32)
+    run_cluster(cluster, mats, "stationary_b")
+    run_cluster(cluster, mats, "stationary_c")
+    assert cluster.check_guards() == 3 * 4                      # A, B and C of every rank
+    torch.testing.assert_close(mats[0][2].full_tensor().double(),
+                               2 * oracle(full_a, full_b, full_c, torch.float32) - full_c.double(), rtol=1e-4, atol=1e-4)
+    c2 = mats[2][2]
+    raw = c2.buffer._raw_local
+    assert raw.numel() == c2.buffer.nbytes + 2 * 512 and c2.buffer.ptr(2) == raw.data_ptr() + 512
+    raw[512 + c2.buffer.nbytes + 7] = 0                          # one byte past the payload of rank 2's C
+    with pytest.raises(ug.GuardViolation, match="rank 2.*above.*payload offset"):
+        cluster.check_guards()
+    plain = ug.EmulatedCluster(2, "cpu")
+    ug.empty(plain.world(0), (8, 8), "row", torch.float32)
+    assert plain.check_guards() == 0                             # no guards unless asked for

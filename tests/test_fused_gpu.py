@@ -373,3 +373,19 @@ def test_dynamic_tile_claiming_many_tiles_per_worker(tile_m, monkeypatch):
         run_program(prog, _dev())
     _status_ok()
     torch.testing.assert_close(c, a.float() @ b.float(), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("method", ["stationary_b", "stationary_c"])
+def test_fused_kernels_stay_inside_their_allocations(method):
+    """Odd shapes on an emulated 4-rank cluster whose symmetric allocations carry guard regions: fetch warps,
+    epilogue stores / red.add into 'peers' and the zeroing kernels must leave every guard byte alone."""
+    m, n, k = 389, 517, 263
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=17, device=_dev())
+    for triple in [("row", "column", "block"), ("block", "block", "block"), ("column", "row", "row")]:
+        cluster = ug.EmulatedCluster(4, _dev(), guard_bytes=4096)
+        mats = build_cluster_matrices(cluster, full_a, full_b, full_c, triple, 1, torch.bfloat16, torch.float32)
+        run_cluster(cluster, mats, method)
+        _status_ok()
+        assert cluster.check_guards() == 12
+        torch.testing.assert_close(mats[0][2].full_tensor().double(), oracle(full_a, full_b, full_c, torch.bfloat16),
+                                   rtol=2e-3, atol=2e-3)

@@ -34,7 +34,7 @@ from .parallel.plan import (  # noqa: F401
     group_ops, select_method,
 )
 from .parallel.symm import (  # noqa: F401
-    CudaIpcWorld, DistComm, EmulatedCluster, FileComm, ShmWorld, SingleWorld, SymmHeap, World,
+    CudaIpcWorld, DistComm, EmulatedCluster, FileComm, GuardViolation, ShmWorld, SingleWorld, SymmHeap, World,
 )
 from .parallel.matrix import DistMatrix, distribute_tensor, empty, resolve, zeros  # noqa: F401
 from .parallel.runtime import (  # noqa: F401

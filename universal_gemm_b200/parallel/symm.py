@@ -20,6 +20,7 @@ from __future__ import annotations
 import ctypes
 import os
 import uuid
+import weakref
 from typing import Sequence
 
 import torch
@@ -31,17 +32,47 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+GUARD_BYTE = 0xA5
+
+
+class GuardViolation(RuntimeError):
+    """Something wrote outside a symmetric allocation (into one of its guard regions)."""
+
+
 class SymmBuffer:
-    """One collective allocation as seen from one rank."""
+    """One collective allocation as seen from one rank.
+
+    With ``guard`` > 0 the raw allocation is ``guard + nbytes + guard`` bytes: the payload sits between two regions
+    filled with ``GUARD_BYTE`` that nothing may touch; ``check_guards`` looks at this rank's copy."""
 
     def __init__(self, world: "World", nbytes: int, ptrs: Sequence[int], tensors: Sequence[torch.Tensor | None],
-                 closer=None):
+                 closer=None, guard: int = 0):
         self.world = world
-        self.nbytes = int(nbytes)
-        self._ptrs = [int(p) for p in ptrs]
-        self._tensors = list(tensors)
+        self.guard = int(guard)
+        self.nbytes = int(nbytes) - 2 * self.guard
+        self._ptrs = [int(p) + self.guard for p in ptrs]
+        self._raw_local = tensors[world.rank] if self.guard else None
+        self._tensors = [t[self.guard:self.guard + self.nbytes] if (t is not None and self.guard) else t for t in tensors]
         self._closer = closer
         self.closed = False
+        if self.guard and self._raw_local is not None:
+            self._raw_local[:self.guard].fill_(GUARD_BYTE)
+            self._raw_local[self.guard + self.nbytes:].fill_(GUARD_BYTE)
+
+    def check_guards(self) -> None:
+        """Raise :class:`GuardViolation` if a byte of this rank's guard regions has changed."""
+        if not self.guard or self._raw_local is None or self.closed:
+            return
+        if self._raw_local.is_cuda:
+            torch.cuda.synchronize(self._raw_local.device)
+        for name, region, base in (("below", self._raw_local[:self.guard], -self.guard),
+                                   ("above", self._raw_local[self.guard + self.nbytes:], self.nbytes)):
+            bad = (region != GUARD_BYTE).nonzero()
+            if bad.numel():
+                first = int(bad[0])
+                raise GuardViolation(f"rank {self.world.rank}: {int(bad.numel())} guard byte(s) {name} a symmetric "
+                                     f"allocation of {self.nbytes} bytes were overwritten, first at payload offset "
+                                     f"{base + first}")
 
     @property
     def local(self) -> torch.Tensor:
@@ -72,8 +103,32 @@ class World:
     device: torch.device
     emulated = False
 
+    # Bytes of guard region on each side of every allocation (a multiple of 256 keeps the payload's alignment);
+    # 0 = none.  Set per world (``world.guard_bytes = 4096`` before the first allocation, same on every rank) or for
+    # all worlds with UGEMM_GUARD_BYTES.  The reference has no sanitizer hook; this is the stand-in for one.
+    guard_bytes: int = _round_up(int(os.environ.get("UGEMM_GUARD_BYTES", "0")), 256)
+
     def alloc(self, nbytes: int) -> SymmBuffer:
+        """Collective allocation of ``nbytes`` per rank (plus guard regions when enabled)."""
+        guard = _round_up(int(self.guard_bytes), 256) if self.guard_bytes else 0
+        buf = self._alloc_raw(_round_up(max(int(nbytes), 1), _ALIGN) + 2 * guard, guard)
+        if guard:
+            live = self.__dict__.setdefault("_guarded", [])
+            live.append(weakref.ref(buf))
+        return buf
+
+    def _alloc_raw(self, nbytes: int, guard: int) -> SymmBuffer:
         raise NotImplementedError
+
+    def check_guards(self) -> int:
+        """Check the guard regions of every live allocation of this rank; returns how many were checked."""
+        n = 0
+        for ref in self.__dict__.get("_guarded", []):
+            buf = ref()
+            if buf is not None and not buf.closed:
+                buf.check_guards()
+                n += 1
+        return n
 
     def barrier(self) -> None:
         """Host-level barrier across the ranks (collective)."""
@@ -198,7 +253,7 @@ class CudaIpcWorld(World):
         torch.cuda.synchronize(self.device)
         self.barrier()
 
-    def alloc(self, nbytes: int) -> SymmBuffer:
+    def _alloc_raw(self, nbytes: int, guard: int) -> SymmBuffer:
         native = self._native
         L = native.lib()
         nbytes = _round_up(max(int(nbytes), 1), _ALIGN)
@@ -235,7 +290,7 @@ class CudaIpcWorld(World):
                 self.comm.barrier()
                 L.ug_free(own)
 
-        buf = SymmBuffer(self, nbytes, ptrs, tensors, closer)
+        buf = SymmBuffer(self, nbytes, ptrs, tensors, closer, guard)
         self._buffers.append(buf)
         return buf
 
@@ -278,7 +333,7 @@ class ShmWorld(World):
     def _path(self, index: int, rank: int) -> str:
         return os.path.join(self._dir, f"ugemm_{self._token}_{index}_{rank}")
 
-    def alloc(self, nbytes: int) -> SymmBuffer:
+    def _alloc_raw(self, nbytes: int, guard: int) -> SymmBuffer:
         nbytes = _round_up(max(int(nbytes), 1), _ALIGN)
         index = self._count
         self._count += 1
@@ -290,7 +345,7 @@ class ShmWorld(World):
         tensors = [torch.from_file(self._path(index, r), shared=True, size=nbytes, dtype=torch.uint8)
                    for r in range(self.size)]
         self.comm.barrier()
-        return SymmBuffer(self, nbytes, [t.data_ptr() for t in tensors], tensors, None)
+        return SymmBuffer(self, nbytes, [t.data_ptr() for t in tensors], tensors, None, guard)
 
     def barrier(self) -> None:
         self.comm.barrier()
@@ -322,11 +377,18 @@ class ShmWorld(World):
 class EmulatedCluster:
     """``size`` ranks inside this process.  ``cluster.world(r)`` is rank r's view."""
 
-    def __init__(self, size: int, device: torch.device | str = "cpu"):
+    def __init__(self, size: int, device: torch.device | str = "cpu", guard_bytes: int | None = None):
         self.size = int(size)
         self.device = torch.device(device)
         self._allocs: list[list[torch.Tensor]] = []
         self._worlds = [EmulatedWorld(self, r) for r in range(self.size)]
+        if guard_bytes is not None:
+            for w in self._worlds:
+                w.guard_bytes = int(guard_bytes)
+
+    def check_guards(self) -> int:
+        """Check every rank's guard regions; returns the number of allocations checked."""
+        return sum(w.check_guards() for w in self._worlds)
 
     def world(self, rank: int) -> "EmulatedWorld":
         return self._worlds[rank]
@@ -355,11 +417,11 @@ class EmulatedWorld(World):
         self._count = 0
         self.timeout_ns = 4_000_000_000
 
-    def alloc(self, nbytes: int) -> SymmBuffer:
+    def _alloc_raw(self, nbytes: int, guard: int) -> SymmBuffer:
         nbytes = _round_up(max(int(nbytes), 1), _ALIGN)
         tensors = self.cluster._get(self._count, nbytes)
         self._count += 1
-        return SymmBuffer(self, nbytes, [t.data_ptr() for t in tensors], tensors, None)
+        return SymmBuffer(self, nbytes, [t.data_ptr() for t in tensors], tensors, None, guard)
 
     def barrier(self) -> None:
         pass
