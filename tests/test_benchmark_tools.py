@@ -88,3 +88,15 @@ def test_trace_summary_on_a_synthetic_timeline():
     ev = TR.to_chrome_trace(arr, pid=3)
     assert {e["name"] for e in ev} == {"load", "main", "epilogue", "fetch"} and all(e["pid"] == 3 for e in ev)
     assert TR.summarize(np.zeros((2, 3, 8), dtype=np.int64)) == {"grid": 2, "recorded_tiles": 0}
+
+
+def test_trace_device_breakdown_adds_up_to_the_kernel_time():
+    from universal_gemm_b200.utils import trace as TR
+
+    s = {"grid": 148, "pair": False, "recorded_tiles": 148 * 10, "kernel_us": 1000.0, "flagwait_us_mean_per_cta": 20.0,
+         "main_loop_share_of_kernel": 0.9, "epilogue_us_mean": 7.0}
+    b = TR.device_breakdown(s)
+    assert abs(sum(b.values()) - 1000e-6) < 1e-12
+    assert abs(b["comm_sync"] - 20e-6) < 1e-12 and abs(b["compute"] - 880e-6) < 1e-12 and abs(b["epilogue"] - 70e-6) < 1e-12
+    assert TR.device_breakdown({"grid": 2, "recorded_tiles": 0}) == {"comm_sync": 0.0, "compute": 0.0, "epilogue": 0.0,
+                                                                    "other": 0.0}

@@ -185,6 +185,38 @@ def to_chrome_trace(arr: np.ndarray, *, pid: int = 0, label: str = "fused") -> l
     return ev
 
 
+def device_breakdown(summary: dict) -> dict:
+    """Split one launch's kernel time the way the host profiler names things (``utils.profile``; reference
+    dtensor_profile.py:1-37), but from the device's own stamps, in seconds, averaged over the CTAs:
+    ``comm_sync`` = producers waiting for staged (remote) chunks, ``compute`` = main loops,
+    ``epilogue`` = exposed part of the epilogues, ``other`` = start-up, tail and idle."""
+    if not summary.get("recorded_tiles"):
+        return {"comm_sync": 0.0, "compute": 0.0, "epilogue": 0.0, "other": 0.0}
+    kernel = summary["kernel_us"] * 1e-6
+    wait = summary.get("flagwait_us_mean_per_cta", 0.0) * 1e-6
+    main = max(summary.get("main_loop_share_of_kernel", 0.0) * kernel - wait, 0.0)
+    workers = summary["grid"] // 2 if summary.get("pair") else summary["grid"]
+    tiles_per_worker = summary["recorded_tiles"] / max(workers, 1)
+    # the epilogue is exposed when the accumulators are single buffered, i.e. when main loops do not fill the kernel
+    epi_total = summary.get("epilogue_us_mean", 0.0) * 1e-6 * tiles_per_worker
+    epi = min(epi_total, max(kernel - main - wait, 0.0))
+    return {"comm_sync": wait, "compute": main, "epilogue": epi, "other": max(kernel - wait - main - epi, 0.0)}
+
+
+def add_to_profile() -> int:
+    """Add the device-side breakdown of every traced program's last launch to the ``utils.profile`` counters
+    (``comm_sync`` and ``compute``; epilogue and idle time count as compute there).  Returns the number of launches."""
+    from . import profile
+
+    n = 0
+    for item in collect():
+        b = device_breakdown(item["summary"])
+        profile.add_comm_sync(b["comm_sync"])
+        profile.add_compute(b["compute"] + b["epilogue"] + b["other"])
+        n += 1
+    return n
+
+
 # ----------------------------------------------------------------------------- collection
 def collect() -> list[dict]:
     """Timelines of the last launch of every traced program that is still alive."""
