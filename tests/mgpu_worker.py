@@ -148,6 +148,15 @@ def main() -> int:
         print(f"[rank {rank}] FAIL addmm hook", flush=True)
     world.barrier()
 
+    try:                                         # guard regions (UGEMM_GUARD_BYTES): nothing wrote outside a shard
+        guarded = world.check_guards()
+    except ug.GuardViolation as exc:
+        guarded = -1
+        failures += 1
+        print(f"[rank {rank}] FAIL {exc}", flush=True)
+    if rank == 0:
+        print(f"mgpu_worker: guarded allocations checked on rank 0: {guarded}", flush=True)
+
     t = torch.tensor([failures], device=dev, dtype=torch.int64)
     dist.all_reduce(t)
     if rank == 0:

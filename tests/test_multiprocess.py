@@ -21,9 +21,10 @@ def _launch(nproc, device, cases, port, timeout=900, extra_env=None):
 
 @pytest.mark.parametrize("nproc", [2, 4])
 def test_cpu_gloo_shared_memory_world(nproc):
-    proc = _launch(nproc, "cpu", "tiny", 29610 + nproc)
+    proc = _launch(nproc, "cpu", "tiny", 29610 + nproc, extra_env={"UGEMM_GUARD_BYTES": "1024"})
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "failures=0" in proc.stdout
+    assert "guarded allocations checked on rank 0: 0" not in proc.stdout
 
 
 @pytest.mark.gpu
@@ -32,6 +33,6 @@ def test_multi_gpu_ipc_world():
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     nproc = 8 if n >= 8 else 4 if n >= 4 else 2
-    proc = _launch(nproc, "cuda", "small", 29650, extra_env={"NCCL_NVLS_ENABLE": "0"})
+    proc = _launch(nproc, "cuda", "small", 29650, extra_env={"NCCL_NVLS_ENABLE": "0", "UGEMM_GUARD_BYTES": "4096"})
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "failures=0" in proc.stdout
