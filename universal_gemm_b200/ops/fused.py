@@ -196,30 +196,35 @@ class FusedProgramBuilder:
             return self.tile_m
         best = None
         for variant in _AUTO_VARIANTS:
-            v = _VARIANTS[variant]
-            workers = self.num_sms // 2 if v["pair"] else self.num_sms
-            if workers < 1:
-                continue
-            per_worker = [0.0] * workers
-            tile = 0
-            for t in self.tasks:
-                kblocks = sum((a.cols + BK - 1) // BK for a, _ in t.segments)
-                tiles = ((t.m + v["rows"] - 1) // v["rows"]) * ((t.n + v["cols"] - 1) // v["cols"])
-                main = kblocks * v["kb_us"]
-                epi = v["epi_us"] * (0.75 if t.c_dtype == native.DT_BF16 else 1.0) \
-                    * (1.5 if t.c_mode == native.C_ADD else 1.0) * (_REMOTE_EPILOGUE_FACTOR if t.c_remote else 1.0)
-                cost = max(main, epi) if v["hidden"] else main + epi
-                full, rest = divmod(tiles, workers)
-                if full:
-                    for w in range(workers):
-                        per_worker[w] += full * cost
-                for _ in range(rest):
-                    per_worker[tile % workers] += cost
-                    tile += 1
-            total = max(per_worker)
-            if best is None or total < best[0]:
+            total = self.model_us(variant)
+            if total is not None and (best is None or total < best[0]):
                 best = (total, variant)
         return best[1] if best else 128
+
+    def model_us(self, variant) -> float | None:
+        """Modelled kernel time in microseconds of the tasks added so far under tile variant ``variant`` (the busiest
+        worker of the model described in :meth:`choose_tile_m`); ``None`` when the variant cannot run here."""
+        v = _VARIANTS[variant]
+        workers = self.num_sms // 2 if v["pair"] else self.num_sms
+        if workers < 1:
+            return None
+        per_worker = [0.0] * workers
+        tile = 0
+        for t in self.tasks:
+            kblocks = sum((a.cols + BK - 1) // BK for a, _ in t.segments)
+            tiles = ((t.m + v["rows"] - 1) // v["rows"]) * ((t.n + v["cols"] - 1) // v["cols"])
+            main = kblocks * v["kb_us"]
+            epi = v["epi_us"] * (0.75 if t.c_dtype == native.DT_BF16 else 1.0) \
+                * (1.5 if t.c_mode == native.C_ADD else 1.0) * (_REMOTE_EPILOGUE_FACTOR if t.c_remote else 1.0)
+            cost = max(main, epi) if v["hidden"] else main + epi
+            full, rest = divmod(tiles, workers)
+            if full:
+                for w in range(workers):
+                    per_worker[w] += full * cost
+            for _ in range(rest):
+                per_worker[tile % workers] += cost
+                tile += 1
+        return max(per_worker)
 
     # ------------------------------------------------------------------ lowering
     def build(self, status_ptr: int) -> FusedProgram:
@@ -446,6 +451,7 @@ class FusedProgramBuilder:
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
                      pieces=len(ordered), staged_bytes=staging_bytes, tile_m=variant if pair else BM,
+                     model_us=round(self.model_us(variant) or 0.0, 1),
                      remote_bytes=sum(st.src.rows * st.src.cols * st.src.elem_bytes for st in staged.values()
                                       if st.src.remote), grid=grid)
         return FusedProgram(device=dev, tables=tables, staging=staging, params=params, grid=grid,
