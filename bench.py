@@ -172,6 +172,8 @@ def run_ours(args) -> dict:
                "host_wall_ms_per_step": max_over_ranks(wall_ms, dev),
                "h2d_bytes_per_step": host_a.numel() * host_a.element_size() * world.size,
                "d2h_bytes_per_step": 4 * world.size, "checksums_read": len(checks),
+               # rate at which each rank's copy stream had to deliver its activations to keep this step time
+               "h2d_gb_per_s_per_gpu": host_a.numel() * host_a.element_size() / (e2e_ms * 1e-3) / 1e9,
                "pipelining": "copy of step i+1 overlaps compute of step i; checksum of step i is read during step i+1"}
     clocks = sampler.stop() if sampler else None
     ug.check_status(dev)
