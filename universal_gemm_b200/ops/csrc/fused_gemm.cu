@@ -42,7 +42,8 @@ namespace {
 //   BM = 128: tile 128 x 256, 4 stages of 48 KiB, two accumulators (epilogue overlaps the next main loop);
 //             96 operand bytes per tensor cycle - best when a tile has few K blocks.
 //   BM = 256: tile 256 x 256 as two 128-row UMMAs that share the B stage, 3 stages of 64 KiB, one accumulator
-//             pair filling TMEM; 64 operand bytes per tensor cycle and 1.5 x the latency cover - best for long K.
+//             pair filling TMEM (the epilogue is exposed); 64 operand bytes per tensor cycle, and a stage feeds
+//             1024 tensor cycles, which covers the issuing thread's per-stage work - best for long K.
 template <int BM>
 struct Cfg {
   static constexpr int kHalves = BM / 128;

@@ -2,8 +2,8 @@
 //
 // Same tables, roles and fetch / remote-accumulate protocol as fused_gemm.cu, but two CTAs of a
 // cluster (two SMs) compute one 256 x 256 output tile together:
-//   * each CTA loads 128 rows of A and 128 of the 256 B columns per K block (32 KiB per stage, 6 stages),
-//     so an SM needs 64 operand bytes per tensor cycle, like the one-CTA 256-row tile;
+//   * each CTA loads 128 rows of A and 128 of the 256 B columns per K block (32 KiB; a stage holds two K blocks,
+//     3 stages of 64 KiB), so an SM needs 64 operand bytes per tensor cycle, like the one-CTA 256-row tile;
 //   * each CTA's TMEM holds its 128 rows x 256 columns, i.e. only half of TMEM, so the accumulators are
 //     double buffered and the epilogue (which may push over NVLink) hides behind the next main loop,
 //     like the one-CTA 128-row tile.
@@ -12,7 +12,9 @@
 // flight feeds twice the tensor time; its 128 x 512 accumulators fill TMEM, so the epilogue is not hidden.
 // CTA rank 0 of the pair issues the UMMAs; TMA loads of both CTAs complete on rank 0's "full" barrier
 // (cp.async.bulk.tensor with .cta_group::2, never multicast); UMMA completion is committed to the
-// "empty" / "accumulator full" barriers of both CTAs with two plain commits.
+// "empty" / "accumulator full" barriers of both CTAs with two plain commits.  With dynamic tile claiming the leader's
+// producer claims tiles and writes them into both CTAs' tile queues (a plain 64-bit store into the other CTA's
+// shared memory).
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
