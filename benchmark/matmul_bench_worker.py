@@ -136,7 +136,10 @@ def bench_case(world, args: argparse.Namespace) -> BenchResult | None:
         err = None
         if args.verify:
             want = full_a.double() @ full_b.double()
-            got = (mats[2].full_tensor(replica=0) if mats is not None else None)
+            if mats is not None:
+                got = mats[2].full_tensor(replica=0)
+            else:                          # plain-DTensor baseline: one more product, gathered (collective)
+                got = torch.matmul(dt_a, dt_b).full_tensor()
             if got is not None:
                 if world.is_cuda:
                     torch.cuda.synchronize()

@@ -100,3 +100,21 @@ def test_trace_device_breakdown_adds_up_to_the_kernel_time():
     assert abs(b["comm_sync"] - 20e-6) < 1e-12 and abs(b["compute"] - 880e-6) < 1e-12 and abs(b["epilogue"] - 70e-6) < 1e-12
     assert TR.device_breakdown({"grid": 2, "recorded_tiles": 0}) == {"comm_sync": 0.0, "compute": 0.0, "epilogue": 0.0,
                                                                     "other": 0.0}
+
+
+@pytest.mark.parametrize("method", ["dtensor", "stationary_c", "stationary_b"])
+def test_plumbing_config_cpu_gloo_1024(tmp_path, method):
+    """The CPU plumbing configuration: C = A @ B, M = N = K = 1024 fp32, A / B / C row-partitioned, replication 1,
+    two gloo ranks, seed 0; the plain-DTensor baseline and both stationary methods give the fp64 product."""
+    result = tmp_path / "result.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29760 + ["dtensor", "stationary_c", "stationary_b"].index(method)),
+           os.path.join(ROOT, "benchmark", "matmul_bench_worker.py"), "--method", method, "--dim-m", "1024",
+           "--dim-n", "1024", "--dim-k", "1024", "--a-partition", "row", "--b-partition", "row", "--c-partition", "row",
+           "--replication-factor", "1", "--warmup-iters", "1", "--measure-iters", "2", "--seed", "0", "--dtype", "fp32",
+           "--device", "cpu", "--verify", "--result-file", str(result)]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    rec = json.loads(result.read_text())
+    assert rec["method"] == method and rec["world_size"] == 2 and (rec["m"], rec["n"], rec["k"]) == (1024, 1024, 1024)
+    assert rec["max_abs_error"] is not None and rec["max_abs_error"] < 1e-2 and rec["median_tflops"] > 0
