@@ -373,26 +373,32 @@ __device__ __forceinline__ void store_chunk_scalar(float* sb, const uint32_t (&v
 // destination vector is gathered from eight 2-byte loads.
 __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
   const int vec_per_row = (pc.row_bytes + 15) >> 4;
+  if (vec_per_row <= 0) return;
   const int64_t total = static_cast<int64_t>(pc.rows) * vec_per_row;
   const char* src = reinterpret_cast<const char*>(pc.src);
   char* dst = reinterpret_cast<char*>(pc.dst);
   if (pc.mode == 0) {
-    // Lanes run along a row, U rows are in flight per lane.  All loads of a batch are issued before
-    // the first store (the compiler barrier keeps the two phases apart), so one warp keeps
-    // U x 512 bytes on the wire.
+    // The piece is walked as one flat sequence of 16-byte vectors (row after row); a warp takes 32 x U consecutive
+    // vectors per batch, whatever the piece's shape (one 24 KiB row or 128 rows of 256 bytes).  All loads of a batch
+    // are issued before the first store (the compiler barrier keeps the two phases apart), so one warp keeps
+    // U x 512 bytes on the wire: over NVLink the copy rate is (bytes in flight) / (about 2 us of latency).
     constexpr int U = 16;
-    for (int r0 = 0; r0 < pc.rows; r0 += U) {
-      for (int c = lane; c < vec_per_row; c += 32) {
-        uint4 buf[U];
-        const char* s0 = src + static_cast<int64_t>(r0) * pc.src_ld + (static_cast<int64_t>(c) << 4);
+    int r = lane / vec_per_row, c = lane - r * vec_per_row;
+    while (r < pc.rows) {
+      uint4 buf[U];
+      int rr = r, cc = c;
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (r0 + u < pc.rows) buf[u] = ld_stream_v4(s0 + u * pc.src_ld);
-        asm volatile("" ::: "memory");
-        char* d0 = dst + static_cast<int64_t>(r0) * pc.dst_ld + (static_cast<int64_t>(c) << 4);
+      for (int u = 0; u < U; ++u) {
+        if (rr < pc.rows) buf[u] = ld_stream_v4(src + rr * pc.src_ld + (static_cast<int64_t>(cc) << 4));
+        cc += 32;
+        while (cc >= vec_per_row) { cc -= vec_per_row; ++rr; }
+      }
+      asm volatile("" ::: "memory");
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (r0 + u < pc.rows) *reinterpret_cast<uint4*>(d0 + u * pc.dst_ld) = buf[u];
+      for (int u = 0; u < U; ++u) {
+        if (r < pc.rows) *reinterpret_cast<uint4*>(dst + r * pc.dst_ld + (static_cast<int64_t>(c) << 4)) = buf[u];
+        c += 32;
+        while (c >= vec_per_row) { c -= vec_per_row; ++r; }
       }
     }
   } else {
