@@ -42,7 +42,6 @@ def main() -> None:
     ap.add_argument("--mib", type=int, default=256, help="payload per transfer")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--cols", type=int, default=8192, help="row length in bf16 elements")
-    ap.add_argument("--probe", action="store_true", help="sweep CTAs / threads / loads in flight of a flat peer copy")
     args = ap.parse_args()
     world = ug.init()
     dev, rank, size = world.device, world.rank, world.size
@@ -63,27 +62,6 @@ def main() -> None:
     ms = timed(world, lambda: st.pull_2d(dst.data_ptr(), cols * 2, src.tile_ptr(rank), src.ld * 2, rows, cols * 2, 2),
                args.iters)
     out["local_copy_kernel_gbs"] = nbytes / ms / 1e6
-
-    if args.probe:
-        import ctypes
-        from universal_gemm_b200.ops import native as nat
-
-        fn = nat.lib().ug_copy_probe
-        fn.restype = ctypes.c_int
-        fn.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
-                       ctypes.c_void_p]
-        table = {}
-        for grid, threads in ((148, 128), (148, 256), (148, 512), (148, 1024), (296, 1024), (1184, 256)):
-            for unroll in (1, 4, 8, 16):
-                code = fn(dst.data_ptr(), src.tile_ptr(peer), nbytes, grid, threads, unroll, ctypes.c_void_p(st.stream()))
-                if code != 0:                 # e.g. too many registers for 1024 threads
-                    torch.cuda.synchronize()
-                    table[f"g{grid}_t{threads}_u{unroll}"] = None
-                    continue
-                ms = timed(world, lambda: fn(dst.data_ptr(), src.tile_ptr(peer), nbytes, grid, threads, unroll,
-                                             ctypes.c_void_p(st.stream())), 5, 1)
-                table[f"g{grid}_t{threads}_u{unroll}"] = round(nbytes / ms / 1e6, 1)
-        out["probe_gbs"] = table
 
     acc = ug.zeros(world, (rows * size // 2, cols), "row", torch.float32)   # fp32: same bytes as above
     part = torch.ones(rows // 2, cols, dtype=torch.float32, device=dev)
@@ -118,6 +96,31 @@ def main() -> None:
     st.check()
     out["fused_fetch_gbs"] = k * cols * 2 / ms / 1e6
     out["fused_fetch_ms"] = ms
+
+    # The same with the A operand remote and rows of 24 KiB (the shape of the staged activations of a
+    # row / column / row GEMM with K = 12288): every copy piece is a single long row.
+    wide_k = 12288
+    wide_rows = max(256, (nbytes // (wide_k * 2)) // 256 * 256)
+    a2 = ug.empty(world, (wide_rows * size, wide_k), "row", torch.bfloat16)
+    a2.local.normal_()
+    b2 = ug.empty(world, (wide_k, 256 * size), "column", torch.bfloat16)
+    b2.local.normal_()
+    c2 = ug.zeros(world, (wide_rows * size, 256), "row", torch.float32)
+    sync_all(world)
+    builder = FusedProgramBuilder(dev, num_sms=st.num_sms)
+    builder.add_task(TaskSpec(c_ptr=c2.tile_ptr(rank), ldc=c2.ld, m=wide_rows, n=256, c_mode=native.C_STORE, c_dtype=0,
+                              segments=[(OperandSlice(a2.tile_ptr(peer), a2.ld, 0, 0, wide_rows, wide_k, remote=True),
+                                         OperandSlice(b2.tile_ptr(rank), b2.ld, 0, 0, wide_k, 256))]))
+    prog2 = builder.build(st.status_ptr)
+
+    def fused_wide():
+        prog2.reset_flags(st.stream())
+        prog2.launch(st.stream())
+
+    ms = timed(world, fused_wide, args.iters)
+    st.check()
+    out["fused_fetch_wide_rows_gbs"] = wide_rows * wide_k * 2 / ms / 1e6
+    out["fused_fetch_wide_rows_ms"] = ms
     if rank == 0:
         print(json.dumps(out), flush=True)
     world.close()

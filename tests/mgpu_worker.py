@@ -20,6 +20,106 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import universal_gemm_b200 as ug  # noqa: E402
 
 
+def large_cases(world) -> tuple[int, int]:
+    """Shapes on which the machinery of the fused kernel runs for real on several GPUs: several waves of tiles per
+    rank, megabytes of staged remote operands, remote stores / red.add of whole tiles, every tile variant with static
+    and dynamic tile order, replication 1 and 2, fp32 and bf16 C; then redistribute and put + signal between GPUs.
+    The status word is checked after every case.  Returns (failures, cases)."""
+    from universal_gemm_b200.parallel.exec import clear_program_cache
+
+    dev, rank, size = world.device, world.rank, world.size
+    failures = ncases = 0
+    configs = [((2048, 3072, 4096), t) for t in (("row", "row", "row"), ("row", "column", "row"),
+                                                 ("column", "row", "row"), ("block", "block", "block"))]
+    configs += [((2048, 12288, 3072), ("row", "column", "row")), ((2048, 3072, 12288), ("column", "row", "row"))]
+    saved = {key: os.environ.get(key) for key in ("UGEMM_TILE_M", "UGEMM_DYNAMIC_TILES")}
+    for (m, n, k), triple in configs:
+        g = torch.Generator().manual_seed(99 + m + n + k)
+        full_a = torch.randn(m, k, generator=g).to(dev)
+        full_b = (torch.randn(k, n, generator=g) / k ** 0.5).to(dev)
+        want = full_a.bfloat16().double() @ full_b.bfloat16().double()
+        scale = max(1.0, want.abs().max().item())
+        for rep, c_dtype in itertools.product([r for r in (1, 2) if size % r == 0], (torch.float32, torch.bfloat16)):
+            a = ug.distribute_tensor(full_a, world, triple[0], rep, dtype=torch.bfloat16)
+            b = ug.distribute_tensor(full_b, world, triple[1], rep, dtype=torch.bfloat16)
+            c = ug.zeros(world, (m, n), triple[2], c_dtype, rep)
+            for variant, dyn, method in itertools.product(("128", "256", "pair", "pair512"), ("0", "1"),
+                                                          ("stationary_c", "stationary_b")):
+                os.environ["UGEMM_TILE_M"], os.environ["UGEMM_DYNAMIC_TILES"] = variant, dyn
+                clear_program_cache()
+                c.local_padded.fill_(7.0)                        # beta = 0 must not depend on what C held
+                torch.cuda.synchronize()
+                world.barrier()
+                for _ in range(2):                               # second call: counters and claims were re-armed
+                    ug.matmul(a, b, c, method=method, beta=0)
+                torch.cuda.synchronize()
+                what = f"{m}x{n}x{k} {triple} rep={rep} {c_dtype} tile={variant} dyn={dyn} {method}"
+                try:
+                    ug.check_status(dev)
+                except Exception as exc:  # noqa: BLE001
+                    failures += 1
+                    print(f"[rank {rank}] status error in {what}: {exc}", flush=True)
+                world.barrier()
+                got = c.full_tensor(replica=0).double()
+                torch.cuda.synchronize()
+                err = (got - want).abs().max().item()
+                tol = (3e-3 if c_dtype == torch.float32 else 3e-2) * scale
+                ncases += 1
+                if not err <= tol:
+                    failures += 1
+                    print(f"[rank {rank}] FAIL {what}: max err {err:.3e} (tolerance {tol:.1e})", flush=True)
+                world.barrier()
+            for mat in (a, b, c):
+                mat.free()
+    for key, val in saved.items():
+        if val is None:
+            os.environ.pop(key, None)
+        else:
+            os.environ[key] = val
+    clear_program_cache()
+
+    # redistribute between partitions over real peers (one-sided pulls), with and without a dtype change
+    full = torch.randn(1531, 2045, generator=torch.Generator().manual_seed(5)).to(dev)
+    src = ug.distribute_tensor(full, world, "block")
+    for part, dtype in (("column", None), ("row", torch.bfloat16)):
+        out = ug.redistribute(src, part, dtype=dtype)
+        torch.cuda.synchronize()
+        world.barrier()
+        got = out.full_tensor()
+        torch.cuda.synchronize()
+        ncases += 1
+        if not torch.equal(got.float(), full if dtype is None else full.bfloat16().float()):
+            failures += 1
+            print(f"[rank {rank}] FAIL redistribute block -> {part} {dtype}", flush=True)
+        world.barrier()
+        out.free()
+    src.free()
+
+    # put + signal: every rank writes a row into its neighbour's window and signals; the receiver's stream waits
+    window = ug.zeros(world, (size, 4096), "row", torch.float32)
+    pad = ug.SignalPad(world, slots=4)
+    dst = (rank + 1) % size
+    payload = torch.full((1, 4000), float(rank + 1), device=dev)
+    ug.put_tile(window, (dst, 0), payload, slice_=ug.Slice2D(ug.Slice1D(0, 1), ug.Slice1D(8, 4008)))
+    pad.signal(dst, slot=1)
+    pad.wait(slot=1, value=1)
+    torch.cuda.synchronize()
+    ncases += 1
+    try:
+        ug.check_status(dev)
+        row = window.local[0]
+        src_rank = (rank - 1) % size
+        if not (bool((row[8:4008] == float(src_rank + 1)).all()) and float(row[:8].abs().sum()) == 0.0
+                and float(row[4008:].abs().sum()) == 0.0):
+            raise AssertionError("window contents differ from what the neighbour put")
+    except Exception as exc:  # noqa: BLE001
+        failures += 1
+        print(f"[rank {rank}] FAIL put + signal: {exc}", flush=True)
+    world.barrier()
+    window.free()
+    return failures, ncases
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--device", default="cuda")
@@ -44,6 +144,11 @@ def main() -> int:
         reps = [r for r in (1, 2) if size % r == 0]
     failures = 0
     ncases = 0
+    if args.cases == "large":
+        f, nc = large_cases(world)
+        failures += f
+        ncases += nc
+        shapes = []
     for (m, n, k), triple, rep, method in itertools.product(shapes, triples, reps, ("stationary_c", "stationary_b")):
         g = torch.Generator().manual_seed(1234 + m + n + k)
         full_a = torch.randn(m, k, generator=g).to(dev)

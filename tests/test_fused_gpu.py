@@ -389,3 +389,76 @@ def test_fused_kernels_stay_inside_their_allocations(method):
         assert cluster.check_guards() == 12
         torch.testing.assert_close(mats[0][2].full_tensor().double(), oracle(full_a, full_b, full_c, torch.bfloat16),
                                    rtol=2e-3, atol=2e-3)
+
+
+def test_beta_zero_with_separate_replica_reduction_clears_every_replica():
+    """beta=0, Stationary-B with a column-partitioned B (no K split), replication 2 and the replica reduction as a
+    separate pass: every replica fills only its share of its own copy of C, so the plan must report that all copies
+    start at zero (stale rows of replica 0 would otherwise survive into the sum)."""
+    from universal_gemm_b200.ops.device import DeviceState
+    from universal_gemm_b200.parallel import exec as X, plan as P, runtime as R
+
+    m, n, k = 512, 384, 320
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=23, device=_dev())
+    cluster = ug.EmulatedCluster(4, _dev())
+    mats = build_cluster_matrices(cluster, full_a, full_b, full_c * 100, ("row", "column", "row"), 2, torch.bfloat16,
+                                  torch.float32)
+    X.clear_program_cache()
+    progs = []
+    for a, b, c in mats:
+        ops = P.build_stationary_b_ops(a.layout, b.layout, c.layout, rank=c.rank)
+        prog, needs_zero = X._program("b", a, b, c, ops, False, 0)
+        assert needs_zero
+        progs.append(prog)
+    st = DeviceState.get(_dev())
+    for _, _, c in mats:                 # what every rank's executor does before its entry barrier
+        c.local_padded.zero_()
+    for prog in progs:                   # the ranks' kernels, one after the other
+        prog.reset_flags(st.stream())
+        prog.launch(st.stream())
+    for _, _, c in mats:
+        R.reduce_replicas(c)
+    _status_ok()
+    want = full_a.bfloat16().double() @ full_b.bfloat16().double()
+    torch.testing.assert_close(mats[0][2].full_tensor(replica=0).double(), want, rtol=2e-3, atol=2e-3)
+    X.clear_program_cache()
+    with pytest.raises(ValueError):      # prepared plans run only the fused kernel: no separate reduction pass
+        ug.prepare_matmul(*mats[0], method="stationary_b", beta=0, fuse_replica_reduce=False)
+
+
+@pytest.mark.parametrize("tile_m", [128, "pair"])
+@pytest.mark.parametrize("field,value", [("a_map", 4000), ("b_flag", 100000), ("seg_count", 77)])
+def test_corrupt_table_entry_is_reported_not_followed(tile_m, field, value):
+    """An index in the device tables that points outside the tables the launch declared (written here by the host,
+    as a truncated or stale table would) is caught by the kernel's own check: it reports UG_ERR_BAD_TABLE, touches
+    nothing through that index and returns; C is left alone and the next launch with intact tables works."""
+    import numpy as np
+
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.device import DeviceState, KernelStatusError
+    from universal_gemm_b200.ops.gemm import build_gemm_program, run_program
+
+    torch.manual_seed(3)
+    m, n, k = 512, 512, 256
+    a = torch.randn(m, k, device=_dev()).bfloat16()
+    b = (torch.randn(k, n, device=_dev()) / k ** 0.5).bfloat16()
+    c = torch.full((m, n), 5.0, device=_dev())
+    prog = build_gemm_program([a], [b], c, mode=native.C_STORE, stage_b=True, tile_m=tile_m)
+    tables = prog._tables
+    is_task = field == "seg_count"
+    dtype = native.TASK_DTYPE if is_task else native.SEGMENT_DTYPE
+    off = (prog.params.tasks if is_task else prog.params.segs) - tables.data_ptr()
+    good = tables[off:off + dtype.itemsize].clone()
+    row = np.frombuffer(good.cpu().numpy().tobytes(), dtype=dtype).copy()
+    row[0][field] = value
+    tables[off:off + dtype.itemsize].copy_(torch.from_numpy(np.frombuffer(row.tobytes(), dtype=np.uint8).copy()))
+    prog.params.timeout_ns = 200_000_000
+    run_program(prog, _dev())
+    torch.cuda.synchronize()
+    with pytest.raises(KernelStatusError) as err:
+        DeviceState.get(_dev()).check()
+    assert err.value.code == native.ERR_BAD_TABLE
+    tables[off:off + dtype.itemsize].copy_(good)
+    run_program(prog, _dev())
+    _status_ok()
+    torch.testing.assert_close(c, a.float() @ b.float(), rtol=2e-3, atol=2e-3)

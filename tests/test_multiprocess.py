@@ -28,11 +28,16 @@ def test_cpu_gloo_shared_memory_world(nproc):
 
 
 @pytest.mark.gpu
-def test_multi_gpu_ipc_world():
+@pytest.mark.parametrize("cases", ["small", "large"])
+def test_multi_gpu_ipc_world(cases):
+    """``small``: all 27 partition triples on an odd shape.  ``large``: shapes with several waves of tiles per rank
+    and megabytes of staged remote operands, for every tile variant, static and dynamic tile order, replication 1
+    and 2, fp32 and bf16 C, plus redistribute and put + signal between GPUs (see mgpu_worker.large_cases)."""
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     nproc = 8 if n >= 8 else 4 if n >= 4 else 2
-    proc = _launch(nproc, "cuda", "small", 29650, extra_env={"NCCL_NVLS_ENABLE": "0", "UGEMM_GUARD_BYTES": "4096"})
+    proc = _launch(nproc, "cuda", cases, 29650 if cases == "small" else 29660,
+                   extra_env={"NCCL_NVLS_ENABLE": "0", "UGEMM_GUARD_BYTES": "4096"})
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "failures=0" in proc.stdout

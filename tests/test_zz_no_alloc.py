@@ -33,7 +33,7 @@ def _call(fn, a, b, c, mode, status):
     stream = torch.cuda.current_stream(c.device).cuda_stream
     code = 0 if c.dtype == torch.float32 else 1
     return fn(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), c.data_ptr(), c.stride(0), c.shape[0], c.shape[1],
-              a.shape[1], code, mode, status.data_ptr(), ctypes.c_void_p(stream))
+              a.shape[1], code, mode, 0 if status is None else status.data_ptr(), ctypes.c_void_p(stream))
 
 
 @pytest.mark.parametrize("m,n,k,pad", [(256, 512, 384, 0),      # aligned: tables only
@@ -82,3 +82,33 @@ def test_noalloc_rejects_what_does_not_fit(capfd):
     assert _call(fn, a, b, c, 1, status) == -1          # atomic mode is not offered here
     torch.cuda.synchronize()
     assert c.min().item() == 7.0 and status.item() == 0  # nothing ran
+
+
+def test_noalloc_leaves_free_memory_unchanged_and_can_keep_its_own_status_word():
+    """The property the entry point exists for: once the first call on the device has done its set-up, further
+    calls change the amount of free device memory by nothing, whether or not operands have to be staged.  The
+    calls here also pass no status word (``status_ptr = 0``): the kernel then reports into a word inside the
+    static array, and the results must still match the regular entry point."""
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.gemm import gemm
+
+    dev = torch.device("cuda", 0)
+    fn = _entry()
+    torch.manual_seed(77)
+    cases = []
+    for m, n, k, pad in ((256, 512, 384, 0), (200, 333, 264, 3)):
+        a = torch.randn(m, k + pad, device=dev).bfloat16()[:, :k]
+        b = (torch.randn(k, n + pad, device=dev) / k ** 0.5).bfloat16()[:, :n]
+        cases.append((a, b, torch.zeros(m, n, device=dev), torch.zeros(m, n, device=dev)))
+    for a, b, _, c_ref in cases:                          # the regular entry point allocates tables and staging
+        gemm(a, b, c_ref, mode=native.C_STORE)
+    assert _call(fn, *cases[0][:3], native.C_STORE, None) == 0      # first call on the device: set-up included
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(dev)[0]
+    for _ in range(2):
+        for a, b, c_new, _ in cases:
+            assert _call(fn, a, b, c_new, native.C_STORE, None) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(dev)[0] == free_before
+    for a, b, c_new, c_ref in cases:
+        torch.testing.assert_close(c_new, c_ref, rtol=2e-3, atol=2e-3)

@@ -30,11 +30,27 @@ struct WaitCtl {
   volatile uint32_t* abort;
   uint32_t* status;
   uint64_t deadline;
+  uint32_t peer_abort;   // shared::cluster address of the abort word of the other CTA of a pair (0: no partner)
 };
 
+// First error wins the status word; the CTA (and its partner in a CTA pair, which would otherwise only leave when
+// its own waits run out) drains and returns.  The partner cannot have exited yet: both CTAs meet at a cluster
+// barrier before they leave.
 __device__ __forceinline__ void raise_error(const WaitCtl& ctl, uint32_t code) {
   atomicCAS(ctl.status, 0u, code);
   *ctl.abort = 1u;
+  if (ctl.peer_abort != 0u) st_shared_cluster_u32(ctl.peer_abort, 1u);
+}
+
+// In-kernel check of the work tables (UG_ERR_BAD_TABLE): indices a tile is about to use must lie inside the tables
+// the launch declared.  A failed check records the error and the tile is never touched.
+__device__ __forceinline__ bool task_in_bounds(const UgFusedParams& P, const UgTask& t) {
+  return t.seg_begin >= 0 && t.seg_count >= 0 && t.seg_begin + t.seg_count <= P.num_segs;
+}
+__device__ __forceinline__ bool segment_in_bounds(const UgFusedParams& P, const UgSegment& sg, int a_flag_last,
+                                                  int b_flag_last) {
+  return sg.a_map >= 0 && sg.a_map < P.num_maps && sg.b_map >= 0 && sg.b_map < P.num_maps && sg.k_len > 0 &&
+         (sg.a_flag < 0 || a_flag_last < P.num_flags) && (sg.b_flag < 0 || b_flag_last < P.num_flags);
 }
 
 // Optional timeline (UgFusedParams::trace != 0): one 64-byte record per (CTA, tile iteration), written by

@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
   ctl.abort = &sh->abort;
   ctl.status = reinterpret_cast<uint32_t*>(P.status);
   ctl.deadline = global_timer_ns() + P.timeout_ns;
+  ctl.peer_abort = 0u;
   // Static schedule: CTA b runs tiles b, b + grid, ...  Dynamic: after its first tile the producer claims the next
   // unclaimed tile from a global counter and hands it to the other roles through sh->tq.
   const bool dyn = P.sched != 0;
@@ -134,6 +135,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
         if (tile >= P.total_tiles) break;
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
+        if (!task_in_bounds(P, t)) { raise_error(ctl, UG_ERR_BAD_TABLE); break; }
         const int tile_n = task_tile_n(t);
         const int n_rem = min(tile_n, t.n - tc.nt * tile_n);
         const int n_chunks = min(4, (n_rem + 63) >> 6);
@@ -143,6 +145,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
         uint64_t waited = 0;
         for (int s = 0; ok && s < t.seg_count; ++s) {
           const UgSegment& sg = segs[t.seg_begin + s];
+          if (!segment_in_bounds(P, sg, sg.a_flag + tc.mt, sg.b_flag + (tc.nt * tile_n) / UG_BN)) {
+            raise_error(ctl, UG_ERR_BAD_TABLE);
+            ok = false;
+            break;
+          }
           const uint64_t w0 = (P.trace != 0 && (sg.a_flag >= 0 || sg.b_flag >= 0)) ? global_timer_ns() : 0;
           if (sg.a_flag >= 0) {
             const int f = sg.a_flag + tc.mt;
@@ -278,6 +285,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       p = __shfl_sync(0xffffffffu, p, 0);
       if (p >= static_cast<uint32_t>(P.num_pieces) || sh->abort) break;
       const UgPiece pc = pieces[p];
+      if (pc.flag < 0 || pc.flag >= P.num_flags) {      // warp-uniform: never copy for a counter that does not exist
+        if (lane == 0) raise_error(ctl, UG_ERR_BAD_TABLE);
+        break;
+      }
       copy_piece(pc, lane);
       __threadfence();
       __syncwarp();

@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
   ctl.abort = &sh->abort;
   ctl.status = reinterpret_cast<uint32_t*>(P.status);
   ctl.deadline = global_timer_ns() + P.timeout_ns;
+  ctl.peer_abort = mapa_shared(smem_u32(const_cast<uint32_t*>(&sh->abort)), rank ^ 1u);
   // Static schedule: pair p runs tiles p, p + pairs, ...  Dynamic: after its first tile the leader CTA's producer
   // claims the next unclaimed tile from a global counter and writes it into the tile queues of both CTAs.
   const bool dyn = P.sched != 0;
@@ -142,6 +143,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
         if (tile >= P.total_tiles) break;
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
+        if (!task_in_bounds(P, t)) { raise_error(ctl, UG_ERR_BAD_TABLE); break; }
         // Tile width 512 (wide kernel only), 256, or 128 for tail tiles.  A tile is 1 or 2 UMMA halves of up to 256
         // columns; of each half this CTA loads its own 128 (64) columns.
         const int tile_n = task_tile_n(t);
@@ -153,6 +155,11 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
         uint64_t waited = 0;
         for (int s = 0; ok && s < t.seg_count; ++s) {
           const UgSegment& sg = segs[t.seg_begin + s];
+          if (!segment_in_bounds(P, sg, sg.a_flag + tc.mt, sg.b_flag + (tc.nt * tile_n) / UG_BN + halves - 1)) {
+            raise_error(ctl, UG_ERR_BAD_TABLE);
+            ok = false;
+            break;
+          }
           const uint64_t w0 = (P.trace != 0 && (sg.a_flag >= 0 || sg.b_flag >= 0)) ? global_timer_ns() : 0;
           if (sg.a_flag >= 0) {
             const int f = sg.a_flag + tc.mt;
@@ -215,6 +222,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
         if (tile < 0 || tile >= P.total_tiles) break;
         const TileCoord tc = locate(tasks, P.num_tasks, tile);
         const UgTask& t = tasks[tc.task];
+        if (!task_in_bounds(P, t)) { raise_error(ctl, UG_ERR_BAD_TABLE); break; }   // this role reads segs[] too
         const int tile_n = task_tile_n(t);
         const int halves = (kWide && min(tile_n, t.n - tc.nt * tile_n) > 256) ? 2 : 1;
         const uint32_t idesc = make_idesc_pair(static_cast<uint32_t>(min(tile_n, 256)));
@@ -306,6 +314,10 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       p = __shfl_sync(0xffffffffu, p, 0);
       if (p >= static_cast<uint32_t>(P.num_pieces) || sh->abort) break;
       const UgPiece pc = pieces[p];
+      if (pc.flag < 0 || pc.flag >= P.num_flags) {      // warp-uniform: never copy for a counter that does not exist
+        if (lane == 0) raise_error(ctl, UG_ERR_BAD_TABLE);
+        break;
+      }
       copy_piece(pc, lane);
       __threadfence();
       __syncwarp();

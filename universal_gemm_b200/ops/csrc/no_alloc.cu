@@ -10,6 +10,9 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "no_alloc.h"
 #include "ugemm_b200.h"
 
@@ -31,8 +34,10 @@ static_assert(kOffPieces + sizeof(UgPiece) * UG_NOALLOC_MAX_PIECES <= UG_NOALLOC
               "piece table overlaps the staging area");
 
 constexpr int kMaxDevices = 64;
-uint64_t g_scratch_addr[kMaxDevices] = {};
+// Published with release / read with acquire: a thread that sees a non-zero address also sees the SM count.
+std::atomic<uint64_t> g_scratch_addr[kMaxDevices];
 int g_num_sms[kMaxDevices] = {};
+std::mutex g_setup_mutex;
 
 constexpr int kPieceBytes = 32 * 1024;
 
@@ -45,7 +50,9 @@ int reject(int code, const char* what) {
 
 // Once per device, with that device current: resolve the device address of the static array.
 int setup_device(int dev) {
-  if (g_scratch_addr[dev] != 0) return 0;
+  if (g_scratch_addr[dev].load(std::memory_order_acquire) != 0) return 0;
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
+  if (g_scratch_addr[dev].load(std::memory_order_acquire) != 0) return 0;
   unsigned char* ptr = nullptr;
   cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
   if (e != cudaSuccess || ptr == nullptr) {
@@ -56,7 +63,7 @@ int setup_device(int dev) {
   e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess || sms <= 0) return UG_NOALLOC_ERR_SETUP;
   g_num_sms[dev] = sms;
-  g_scratch_addr[dev] = reinterpret_cast<uint64_t>(ptr);
+  g_scratch_addr[dev].store(reinterpret_cast<uint64_t>(ptr), std::memory_order_release);
   return 0;
 }
 
@@ -87,7 +94,7 @@ extern "C" int ug_gemm_noalloc(uint64_t a, int64_t lda, uint64_t b, int64_t ldb,
   if (dev < 0 || dev >= kMaxDevices) return reject(UG_NOALLOC_ERR_INVALID, "device index out of range");
   int rc = setup_device(dev);
   if (rc != 0) return rc;
-  const uint64_t S = g_scratch_addr[dev];
+  const uint64_t S = g_scratch_addr[dev].load(std::memory_order_acquire);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   const Operand A{a, lda, m, k}, B{b, ldb, k, n};
@@ -206,6 +213,7 @@ extern "C" int ug_gemm_noalloc(uint64_t a, int64_t lda, uint64_t b, int64_t ldb,
   P.status = status_ptr != 0 ? status_ptr : S + kOffStatus;
   P.num_maps = 2;
   P.num_tasks = 1;
+  P.num_segs = 1;
   P.num_pieces = num_pieces;
   P.num_flags = num_flags;
   P.total_tiles = m_tiles * n_tiles;

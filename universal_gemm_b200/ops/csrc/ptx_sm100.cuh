@@ -63,12 +63,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, uint64_t map_addr
       : "memory");
 }
 
-// Ask TMA to bring one box into L2 only (no shared-memory destination, no completion signal).
-__device__ __forceinline__ void tma_prefetch_l2_2d(uint64_t map_addr, int32_t x, int32_t y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map_addr), "r"(x), "r"(y)
-               : "memory");
-}
-
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result),
@@ -142,6 +136,9 @@ __device__ __forceinline__ void cluster_sync_all() {
 // 64-bit store into the shared memory of a CTA of the cluster (shared::cluster address from mapa_shared).
 __device__ __forceinline__ void st_shared_cluster_u64(uint32_t cluster_addr, unsigned long long v) {
   asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(cluster_addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 // Arrive on an mbarrier that may live in the other CTA of the cluster (shared::cluster address).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {

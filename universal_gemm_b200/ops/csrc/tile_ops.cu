@@ -153,26 +153,6 @@ __global__ void __launch_bounds__(kThreads) convert_2d_kernel(D* dst, int64_t ds
   }
 }
 
-// Flat copy with a chosen number of CTAs, threads and 16-byte loads in flight per thread: the
-// tuning probe behind the fetch-warp configuration of the fused kernel (bandwidth vs. bytes in flight).
-template <int U>
-__global__ void copy_probe_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int64_t nvec) {
-  const int64_t span = static_cast<int64_t>(blockDim.x) * U;
-  for (int64_t base = static_cast<int64_t>(blockIdx.x) * span; base < nvec; base += static_cast<int64_t>(gridDim.x) * span) {
-    uint4 buf[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x + threadIdx.x;
-      if (i < nvec) buf[u] = ld_stream_v4(src + i);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t i = base + static_cast<int64_t>(u) * blockDim.x + threadIdx.x;
-      if (i < nvec) dst[i] = buf[u];
-    }
-  }
-}
-
 // Eight elements per thread with 16-byte accesses on the 2-byte side (both sides 16-byte aligned, cols % 8 == 0).
 __global__ void __launch_bounds__(kThreads) convert_f32_to_bf16_vec_kernel(__nv_bfloat16* dst, int64_t dst_ld,
                                                                            const float* src, int64_t src_ld,
@@ -299,24 +279,5 @@ extern "C" int ug_convert_2d(uint64_t dst, int64_t dst_ld_elems, int32_t dst_dty
   else if (dst_dtype == 1 && src_dtype == 1) UG_CVT(__nv_bfloat16, __nv_bfloat16);
   else return static_cast<int>(cudaErrorInvalidValue);
 #undef UG_CVT
-  return static_cast<int>(cudaGetLastError());
-}
-
-extern "C" int ug_copy_probe(uint64_t dst, uint64_t src, int64_t bytes, int32_t grid, int32_t threads, int32_t unroll,
-                             void* stream) {
-  if ((dst & 15) || (src & 15) || (bytes & 15) || grid <= 0 || threads <= 0 || threads > 1024)
-    return static_cast<int>(cudaErrorInvalidValue);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  uint4* d = reinterpret_cast<uint4*>(dst);
-  const uint4* s = reinterpret_cast<const uint4*>(src);
-  const int64_t nvec = bytes >> 4;
-  switch (unroll) {
-    case 1: copy_probe_kernel<1><<<grid, threads, 0, st>>>(d, s, nvec); break;
-    case 2: copy_probe_kernel<2><<<grid, threads, 0, st>>>(d, s, nvec); break;
-    case 4: copy_probe_kernel<4><<<grid, threads, 0, st>>>(d, s, nvec); break;
-    case 8: copy_probe_kernel<8><<<grid, threads, 0, st>>>(d, s, nvec); break;
-    case 16: copy_probe_kernel<16><<<grid, threads, 0, st>>>(d, s, nvec); break;
-    default: return static_cast<int>(cudaErrorInvalidValue);
-  }
   return static_cast<int>(cudaGetLastError());
 }

@@ -82,7 +82,7 @@ typedef struct {
   int32_t total_tiles;
   int32_t tile_m;         // rows per output tile: 128 (0 means 128) or 256
   uint64_t timeout_ns;    // limit of every in-kernel wait
-  int32_t prefetch_kblocks;  // unused (L2 prefetch by the TMA producer measured slower at every distance); keep 0
+  int32_t num_segs;          // entries of `segs` (for the in-kernel table check)
   int32_t cta_pair;          // 1: tables were lowered for the CTA-pair kernel (ug_fused_gemm_pair)
   uint64_t trace;            // 0 = off; else uint64[grid][trace_slots + 1][UG_TR_FIELDS] timeline records (see UG_TR_*)
   int32_t trace_slots;       // tile iterations recorded per CTA (later ones are dropped)
@@ -162,11 +162,6 @@ int ug_accumulate_2d(uint64_t dst, int64_t dst_ld_elems, uint64_t src, int64_t s
 // src_dtype / dst_dtype: 0 fp32, 1 bf16.
 int ug_convert_2d(uint64_t dst, int64_t dst_ld_elems, int32_t dst_dtype, uint64_t src,
                   int64_t src_ld_elems, int32_t src_dtype, int32_t rows, int32_t cols, void* stream);
-
-// Tuning probe: flat 16-byte-vector copy with `grid` CTAs of `threads` threads and `unroll` loads in
-// flight per thread (1, 2, 4, 8 or 16); src may be peer memory.
-int ug_copy_probe(uint64_t dst, uint64_t src, int64_t bytes, int32_t grid, int32_t threads, int32_t unroll,
-                  void* stream);
 
 #ifdef __cplusplus
 }

@@ -439,7 +439,7 @@ class FusedProgramBuilder:
         params.total_tiles = total_tiles
         params.tile_m = BM
         params.cta_pair = 2 if wide else (1 if pair else 0)
-        params.prefetch_kblocks = 0
+        params.num_segs = len(seg_rows)
         # Dynamic tile claiming (two uint32 counters, re-armed by the kernel itself).  Default: on for the CTA-pair
         # variants, where it measured +6-9 % on the headline GEMM (workers finish 90 us apart instead of 450 us); off
         # for the one-CTA variants, where it measured level: under the power cap the SMs that finish early leave their

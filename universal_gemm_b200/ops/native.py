@@ -80,7 +80,7 @@ class FusedParams(ctypes.Structure):
         ("num_maps", c_int32), ("num_tasks", c_int32), ("num_pieces", c_int32), ("num_flags", c_int32),
         ("total_tiles", c_int32), ("tile_m", c_int32),
         ("timeout_ns", c_uint64),
-        ("prefetch_kblocks", c_int32), ("cta_pair", c_int32),
+        ("num_segs", c_int32), ("cta_pair", c_int32),
         ("trace", c_uint64), ("trace_slots", c_int32), ("epi_poll_ns", c_int32),
         ("sched", c_uint64),
     ]

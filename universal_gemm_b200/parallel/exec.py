@@ -71,7 +71,10 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
     push_to_origin = fuse_replica_reduce and rep_c > 1
     # One writer per C element: Stationary-C without replicated C (the owner computes the whole K range),
     # Stationary-B whose B is not split along K (each B tile owner covers all of K for its rows / columns).
-    single_writer = (kind == "c" and rep_c == 1) or (kind == "b" and T.grid_shape(b.layout)[0] == 1)
+    # With a separate replica reduction (replicated C, nothing pushed to replica 0 by the epilogue) every replica
+    # fills only its share of its own copy and the reduction then adds whole tiles, so all copies must start at zero.
+    single_writer = ((kind == "c" and rep_c == 1) or (kind == "b" and T.grid_shape(b.layout)[0] == 1)) \
+        and not (rep_c > 1 and not fuse_replica_reduce)
     needs_zero = beta == 0 and not single_writer
 
     buffers = (a.buffer, b.buffer, c.buffer)

@@ -13,6 +13,7 @@ DTensors allocate from NVSHMEM (``DTensor.nvshmem_base()``, dtensor_utils.py:360
 """
 from __future__ import annotations
 
+import weakref
 from typing import Any
 
 import torch
@@ -28,7 +29,8 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
-_registry: dict[int, "DistMatrix"] = {}
+# Local data pointer -> matrix, weakly: a matrix that nobody references any more drops out by itself.
+_registry: "weakref.WeakValueDictionary[int, DistMatrix]" = weakref.WeakValueDictionary()
 
 
 class DistMatrix:
@@ -140,7 +142,7 @@ class DistMatrix:
             dt = DTensor.from_local(self.local, mesh, conv, run_check=False, shape=torch.Size(self.shape),
                                     stride=(self.shape[1], 1))
             self._dtensor = dt
-            _registry[id(dt)] = self
+            dt._ug_matrix = self          # the DTensor keeps its matrix alive and names it directly
             _registry[dt._local_tensor.data_ptr()] = self
         return self._dtensor
 
@@ -151,7 +153,9 @@ class DistMatrix:
         _exec.drop_programs_for(self.buffer.ptr(self.rank))
         _registry.pop(self.buffer.ptr(self.rank), None)
         if self._dtensor is not None:
-            _registry.pop(id(self._dtensor), None)
+            _registry.pop(self._dtensor._local_tensor.data_ptr(), None)
+            self._dtensor._ug_matrix = None
+            self._dtensor = None
         self.buffer.free()
 
     def __repr__(self) -> str:
@@ -163,8 +167,8 @@ def resolve(x: Any) -> DistMatrix:
     """Return the :class:`DistMatrix` behind ``x`` (itself, or a DTensor made by ``to_dtensor``)."""
     if isinstance(x, DistMatrix):
         return x
-    hit = _registry.get(id(x))
-    if hit is None and hasattr(x, "_local_tensor"):
+    hit = getattr(x, "_ug_matrix", None)
+    if hit is None and hasattr(x, "_local_tensor"):     # e.g. a DTensor derived from the one to_dtensor() made
         hit = _registry.get(x._local_tensor.data_ptr())
     if hit is None:
         raise RuntimeError(

@@ -29,6 +29,11 @@ class MatmulPlan:
         self.ops = build(self.a.layout, self.b.layout, self.c.layout, rank=self.c.rank)
         self.beta = beta
         self.fuse = fuse_replica_reduce
+        if not fuse_replica_reduce and X.T.replication_factor(self.c.layout) > 1:
+            # run() / capture() queue only the fused kernel and its barriers; the separate reduction pass of the
+            # executor (zero the non-origin replicas, reduce_replicas, barrier) is not part of a prepared plan.
+            raise ValueError("a prepared plan of a replicated C needs fuse_replica_reduce=True "
+                             "(use ug.matmul(..., fuse_replica_reduce=False) for the separate reduction pass)")
         # lowering happens here; later calls hit the program cache by identity of the op list
         self.program, self.needs_zero = X._program(self.kind, self.a, self.b, self.c, self.ops, self.fuse, beta)
         self._graph: torch.cuda.CUDAGraph | None = None
