@@ -82,22 +82,7 @@ def main() -> None:
     from universal_gemm_b200.ops import native
     from universal_gemm_b200.ops.fused import FusedProgramBuilder, OperandSlice, TaskSpec
 
-    builder = FusedProgramBuilder(dev, num_sms=st.num_sms)
-    builder.add_task(TaskSpec(c_ptr=c.tile_ptr(rank), ldc=c.ld, m=128, n=cols, c_mode=native.C_STORE, c_dtype=0,
-                              segments=[(OperandSlice(a.tile_ptr(rank), a.ld, 0, 0, 128, k),
-                                         OperandSlice(bmat.tile_ptr(peer), bmat.ld, 0, 0, k, cols, remote=True))]))
-    prog = builder.build(st.status_ptr)
-
-    def fused():
-        prog.reset_flags(st.stream())
-        prog.launch(st.stream())
-
-    ms = timed(world, fused, args.iters)
-    st.check()
-    out["fused_fetch_gbs"] = k * cols * 2 / ms / 1e6
-    out["fused_fetch_ms"] = ms
-
-    # The same with the A operand remote and rows of 24 KiB (the shape of the staged activations of a
+    # Second case: the A operand remote with rows of 24 KiB (the shape of the staged activations of a
     # row / column / row GEMM with K = 12288): every copy piece is a single long row.
     wide_k = 12288
     wide_rows = max(256, (nbytes // (wide_k * 2)) // 256 * 256)
@@ -107,20 +92,35 @@ def main() -> None:
     b2.local.normal_()
     c2 = ug.zeros(world, (wide_rows * size, 256), "row", torch.float32)
     sync_all(world)
-    builder = FusedProgramBuilder(dev, num_sms=st.num_sms)
-    builder.add_task(TaskSpec(c_ptr=c2.tile_ptr(rank), ldc=c2.ld, m=wide_rows, n=256, c_mode=native.C_STORE, c_dtype=0,
-                              segments=[(OperandSlice(a2.tile_ptr(peer), a2.ld, 0, 0, wide_rows, wide_k, remote=True),
-                                         OperandSlice(b2.tile_ptr(rank), b2.ld, 0, 0, wide_k, 256))]))
-    prog2 = builder.build(st.status_ptr)
+    # Both for every tile variant: the copy loop is compiled into each kernel instantiation separately.
+    for variant in (128, 256, "pair", "pair512"):
+        builder = FusedProgramBuilder(dev, num_sms=st.num_sms, tile_m=variant)
+        builder.add_task(TaskSpec(c_ptr=c.tile_ptr(rank), ldc=c.ld, m=128, n=cols, c_mode=native.C_STORE, c_dtype=0,
+                                  segments=[(OperandSlice(a.tile_ptr(rank), a.ld, 0, 0, 128, k),
+                                             OperandSlice(bmat.tile_ptr(peer), bmat.ld, 0, 0, k, cols, remote=True))]))
+        prog = builder.build(st.status_ptr)
 
-    def fused_wide():
-        prog2.reset_flags(st.stream())
-        prog2.launch(st.stream())
+        def fused(prog=prog):
+            prog.reset_flags(st.stream())
+            prog.launch(st.stream())
 
-    ms = timed(world, fused_wide, args.iters)
-    st.check()
-    out["fused_fetch_wide_rows_gbs"] = wide_rows * wide_k * 2 / ms / 1e6
-    out["fused_fetch_wide_rows_ms"] = ms
+        ms = timed(world, fused, args.iters)
+        st.check()
+        out[f"fused_fetch_gbs_{variant}"] = round(k * cols * 2 / ms / 1e6, 1)
+
+        builder = FusedProgramBuilder(dev, num_sms=st.num_sms, tile_m=variant)
+        builder.add_task(TaskSpec(c_ptr=c2.tile_ptr(rank), ldc=c2.ld, m=wide_rows, n=256, c_mode=native.C_STORE, c_dtype=0,
+                                  segments=[(OperandSlice(a2.tile_ptr(peer), a2.ld, 0, 0, wide_rows, wide_k, remote=True),
+                                             OperandSlice(b2.tile_ptr(rank), b2.ld, 0, 0, wide_k, 256))]))
+        prog2 = builder.build(st.status_ptr)
+
+        def fused_wide(prog2=prog2):
+            prog2.reset_flags(st.stream())
+            prog2.launch(st.stream())
+
+        ms = timed(world, fused_wide, args.iters)
+        st.check()
+        out[f"fused_fetch_wide_rows_gbs_{variant}"] = round(wide_rows * wide_k * 2 / ms / 1e6, 1)
     if rank == 0:
         print(json.dumps(out), flush=True)
     world.close()

@@ -395,26 +395,30 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
   char* dst = reinterpret_cast<char*>(pc.dst);
   if (pc.mode == 0) {
     // The piece is walked as one flat sequence of 16-byte vectors (row after row); a warp takes 32 x U consecutive
-    // vectors per batch, whatever the piece's shape (one 24 KiB row or 128 rows of 256 bytes).  All loads of a batch
-    // are issued before the first store (the compiler barrier keeps the two phases apart), so one warp keeps
-    // U x 512 bytes on the wire: over NVLink the copy rate is (bytes in flight) / (about 2 us of latency).
-    constexpr int U = 16;
-    int r = lane / vec_per_row, c = lane - r * vec_per_row;
-    while (r < pc.rows) {
+    // vectors per batch, whatever the piece's shape (one 24 KiB row or 128 rows of 256 bytes).  The batch is
+    // straight-line code: U unconditional loads (lanes past the end re-read the last vector), a compiler barrier,
+    // then the predicated stores, so one warp keeps U x 512 bytes on the wire: over NVLink the copy rate is
+    // (bytes in flight) / (about 2 us of latency), and a copy loop whose loads are issued one at a time reaches
+    // a quarter of the link rate.
+    constexpr uint32_t U = 16;
+    const uint32_t vpr = static_cast<uint32_t>(vec_per_row);
+    const uint32_t nvec = static_cast<uint32_t>(total);
+    for (uint32_t base = 0; base < nvec; base += 32u * U) {
       uint4 buf[U];
-      int rr = r, cc = c;
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (rr < pc.rows) buf[u] = ld_stream_v4(src + rr * pc.src_ld + (static_cast<int64_t>(cc) << 4));
-        cc += 32;
-        while (cc >= vec_per_row) { cc -= vec_per_row; ++rr; }
+      for (uint32_t u = 0; u < U; ++u) {
+        const uint32_t idx = min(base + u * 32u + static_cast<uint32_t>(lane), nvec - 1u);
+        const uint32_t r = idx / vpr, c = idx - r * vpr;
+        buf[u] = ld_stream_v4(src + static_cast<int64_t>(r) * pc.src_ld + (static_cast<int64_t>(c) << 4));
       }
       asm volatile("" ::: "memory");
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (r < pc.rows) *reinterpret_cast<uint4*>(dst + r * pc.dst_ld + (static_cast<int64_t>(c) << 4)) = buf[u];
-        c += 32;
-        while (c >= vec_per_row) { c -= vec_per_row; ++r; }
+      for (uint32_t u = 0; u < U; ++u) {
+        const uint32_t idx = base + u * 32u + static_cast<uint32_t>(lane);
+        if (idx < nvec) {
+          const uint32_t r = idx / vpr, c = idx - r * vpr;
+          *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * pc.dst_ld + (static_cast<int64_t>(c) << 4)) = buf[u];
+        }
       }
     }
   } else {
