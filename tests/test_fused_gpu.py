@@ -462,3 +462,28 @@ def test_corrupt_table_entry_is_reported_not_followed(tile_m, field, value):
     run_program(prog, _dev())
     _status_ok()
     torch.testing.assert_close(c, a.float() @ b.float(), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("offset,n", [(1, 1537), (2, 700), (3, 256), (1, 5), (3, 67)])
+@pytest.mark.parametrize("mode", ["store", "add", "atomic"])
+@pytest.mark.parametrize("tile_m", [128, 256, "pair", "pair512"])
+def test_gemm_kernel_c_region_on_odd_columns(offset, n, mode, tile_m):
+    """C is a column range that starts on an odd column of a wider, 16-byte-pitched matrix (what a column or block
+    partition of an odd-sized C gives): the epilogue writes head columns singly and the rest as 16-byte vectors, and
+    must not touch the columns next to the region."""
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.gemm import gemm
+
+    torch.manual_seed(offset * 1000 + n)
+    m, k = 300, 200
+    a = torch.randn(m, k, device=_dev()).bfloat16()
+    b = (torch.randn(k, n, device=_dev()) / k ** 0.5).bfloat16()
+    pitch = (offset + n + 7 + 63) // 64 * 64
+    big0 = torch.randn(m, pitch, device=_dev())
+    big = big0.clone()
+    c = big[:, offset:offset + n]
+    gemm(a, b, c, mode={"store": native.C_STORE, "add": native.C_ADD, "atomic": native.C_ATOMIC}[mode], tile_m=tile_m)
+    _status_ok()
+    ref = a.float() @ b.float() + (0 if mode == "store" else big0[:, offset:offset + n])
+    torch.testing.assert_close(c, ref, rtol=2e-3, atol=2e-3)
+    assert torch.equal(big[:, :offset], big0[:, :offset]) and torch.equal(big[:, offset + n:], big0[:, offset + n:])

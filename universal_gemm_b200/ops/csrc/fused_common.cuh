@@ -161,6 +161,9 @@ __device__ __forceinline__ int task_tile_n(const UgTask& t) {
   return v > 0 ? v : UG_BN;
 }
 __device__ __forceinline__ bool task_c_vec(const UgTask& t) { return (t.c_vec & 1) != 0; }
+// Bit 1 of c_vec: the row pitch of C is a multiple of 16 bytes (and C is element-aligned), so every row of a region
+// has the same alignment phase even when the region starts on an odd column.
+__device__ __forceinline__ bool task_c_pitch_vec(const UgTask& t) { return (t.c_vec & 2) != 0; }
 
 struct TileCoord {
   int task;
@@ -383,6 +386,115 @@ __device__ __forceinline__ void store_chunk_scalar(float* sb, const uint32_t (&v
   __syncwarp();
 }
 
+// The same transpose for a 32-column chunk of which only columns [lo, hi) are to be written (lo a multiple of 4;
+// c_base 16-byte aligned): whole 16-byte groups inside the range go out as vectors, the ragged end element by element.
+__device__ __forceinline__ void store_chunk_f32_ragged(float* sb, const uint32_t (&v)[32], int lane, float* c_base,
+                                                       int64_t ldc, int rows_valid, int mode, int lo, int hi) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<uint4*>(sb + epi_off(lane, j)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  __syncwarp();
+  const int rsub = lane >> 3, cseg = (lane & 7) * 4;
+  if (cseg >= lo && cseg < hi) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = i * 4 + rsub;
+      if (r < rows_valid) {
+        float4 x = *reinterpret_cast<const float4*>(sb + epi_off(r, lane & 7));
+        float* g = c_base + r * ldc + cseg;
+        if (cseg + 4 <= hi) {
+          float4* g4 = reinterpret_cast<float4*>(g);
+          if (mode == 1) {
+            red_add_v4_f32(g4, x.x, x.y, x.z, x.w);
+          } else {
+            if (mode == 0) {
+              const float4 old = *g4;
+              x.x += old.x; x.y += old.y; x.z += old.z; x.w += old.w;
+            }
+            *g4 = x;
+          }
+        } else {
+          const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int e = 0; e < 3; ++e) {
+            if (cseg + e < hi) {
+              if (mode == 1) red_add_f32(g + e, xs[e]);
+              else if (mode == 0) g[e] += xs[e];
+              else g[e] = xs[e];
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+}
+
+// fp32 C whose rows are 16 bytes apart in phase but whose region starts on any column (odd-shaped partitions) and has
+// any width: up to three head columns go out element by element, then 32-column chunks that start on a 16-byte
+// boundary of C.  `avail` TMEM columns can be read from `taddr`; a last chunk that would read past them is moved back
+// by a multiple of four columns and writes only what the chunks before it have not written.
+__device__ __forceinline__ void epilogue_drain_f32_shifted(uint32_t taddr, const UgTask& t, int row0, int col0,
+                                                           int n_rem, int avail, float* epi_buf, int lane) {
+  const int rows_valid = min(32, t.m - row0);
+  float* c_row = reinterpret_cast<float*>(t.c_ptr) + static_cast<int64_t>(row0) * t.ldc + col0;
+  const int phase = static_cast<int>((reinterpret_cast<uint64_t>(c_row) >> 2) & 3u);
+  const int head = min((4 - phase) & 3, n_rem);
+  uint32_t v[32];
+  if (head > 0) {
+    tmem_ld_32x32(taddr, v);
+    tmem_ld_wait();
+    if (lane < rows_valid) {
+      float* g = c_row + lane * t.ldc;
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        if (j < head) {
+          const float x = __uint_as_float(v[j]);
+          if (t.c_mode == 1) red_add_f32(g + j, x);
+          else if (t.c_mode == 0) g[j] += x;
+          else g[j] = x;
+        }
+      }
+    }
+  }
+  int c = head;
+  for (; c < n_rem && c + 32 <= avail; c += 32) {
+    tmem_ld_32x32(taddr + c, v);
+    tmem_ld_wait();
+    store_chunk_f32_ragged(epi_buf, v, lane, c_row + c, t.ldc, rows_valid, t.c_mode, 0, min(32, n_rem - c));
+  }
+  if (c < n_rem) {
+    // Fewer than 32 columns are left and a chunk on this boundary would read past the readable TMEM columns: move it
+    // back by a multiple of four columns (it then skips what is written already); up to three columns can remain
+    // beyond its end, they go out element by element from a chunk that ends with the region.
+    const int lo = (c + 32 - avail + 3) & ~3;
+    const int start = c - lo;
+    const int hi = min(32, n_rem - start);
+    if (lo < hi) {
+      tmem_ld_32x32(taddr + start, v);
+      tmem_ld_wait();
+      store_chunk_f32_ragged(epi_buf, v, lane, c_row + start, t.ldc, rows_valid, t.c_mode, lo, hi);
+    }
+    const int rem = n_rem - min(start + 32, n_rem);
+    if (rem > 0) {
+      tmem_ld_32x32(taddr + n_rem - 32, v);
+      tmem_ld_wait();
+      if (lane < rows_valid) {
+        float* g = c_row + lane * t.ldc + n_rem - 32;
+#pragma unroll
+        for (int j = 29; j < 32; ++j) {
+          if (j >= 32 - rem) {
+            const float x = __uint_as_float(v[j]);
+            if (t.c_mode == 1) red_add_f32(g + j, x);
+            else if (t.c_mode == 0) g[j] += x;
+            else g[j] = x;
+          }
+        }
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- fetch warps
 // Copy one piece with the 32 lanes of a warp.  mode 0: 16-byte vectors, sixteen in
 // flight per lane.  mode 1: the source is only 2-byte aligned; every 16-byte
@@ -445,8 +557,12 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
 // columns col0.. of the task's C.  The common case (fp32 C, 16-byte aligned, whole 32-column chunks) is software
 // pipelined: the TMEM load of the next chunk is in flight while the current chunk goes through shared memory.
 __device__ __forceinline__ void epilogue_drain(uint32_t taddr, const UgTask& t, int row0, int col0, int n_rem,
-                                               float* epi_buf, int lane) {
+                                               int avail, float* epi_buf, int lane) {
   const int rows_valid = min(32, t.m - row0);               // <= 0 when the warp is past the region
+  if (t.c_dtype == 0 && task_c_pitch_vec(t) && !(task_c_vec(t) && (n_rem & 31) == 0 && (col0 & 3) == 0)) {
+    epilogue_drain_f32_shifted(taddr, t, row0, col0, n_rem, avail, epi_buf, lane);
+    return;
+  }
   if (task_c_vec(t) && t.c_dtype == 0 && (n_rem & 31) == 0) {
     float* c_row = reinterpret_cast<float*>(t.c_ptr) + static_cast<int64_t>(row0) * t.ldc + col0;
     uint32_t va[32], vb[32];

@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
         if (cn <= 0 || tc.mt * BM + h * 128 >= t.m) break;     // nothing to do (warp-uniform)
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                (C::kAccBufs == 2 ? acc * UG_BN : static_cast<uint32_t>(h) * UG_BN);
-        epilogue_drain(taddr + c0, t, tc.mt * BM + h * 128 + quad * 32, col0 + c0, cn, epi_buf, lane);
+        epilogue_drain(taddr + c0, t, tc.mt * BM + h * 128 + quad * 32, col0 + c0, cn, UG_BN - c0, epi_buf, lane);
       }
       if (tracer) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
       tc_fence_before();

@@ -306,6 +306,8 @@ class FusedProgramBuilder:
                 kblocks += (a.cols + BK - 1) // BK
             c_elem = 4 if task.c_dtype == native.DT_F32 else 2
             c_vec = int(task.c_ptr % 16 == 0 and (task.ldc * c_elem) % 16 == 0)
+            if task.c_ptr % c_elem == 0 and (task.ldc * c_elem) % 16 == 0:
+                c_vec |= 2          # rows share one alignment phase: vector stores from the next 16-byte boundary on
             if task.tile_n != BN:
                 c_vec |= task.tile_n << 16
             band = 2048 // BM
