@@ -57,6 +57,15 @@ class BenchResult:
     timing: str = "cuda_events_max_over_ranks"
     executed_method: str = ""
     max_abs_error: float | None = None
+    verified_rows: int | None = None
+    # bytes rank 0 moves over NVLink per iteration (staged remote operand slices in, partial C out), the tile variant
+    # its plan was lowered to, and the roofline time of the case: the slower of its FLOPs at the measured bf16 GEMM
+    # peak of one GPU and its remote bytes at the measured peer-copy rate per direction
+    remote_in_bytes: int | None = None
+    remote_out_bytes: int | None = None
+    tile_variant: str = ""
+    roofline_seconds: float | None = None
+    roofline_fraction: float | None = None
 
 
 def _dtensor_iteration(dt_a, dt_b):
@@ -133,22 +142,50 @@ def bench_case(world, args: argparse.Namespace) -> BenchResult | None:
         if world.is_cuda:
             ug.check_status(dev)
 
-        err = None
+        err, verified_rows = None, None
         if args.verify:
-            want = full_a.double() @ full_b.double()
             if mats is not None:
                 got = mats[2].full_tensor(replica=0)
             else:                          # plain-DTensor baseline: one more product, gathered (collective)
                 got = torch.matmul(dt_a, dt_b).full_tensor()
-            if got is not None:
-                if world.is_cuda:
-                    torch.cuda.synchronize()
-                err = float((got.double() - want).abs().max().item())
+            nrows = int(getattr(args, "verify_rows", 0) or 0)
+            if 0 < nrows < m:              # sampled rows (a different sample per case): cheap enough for every case
+                rows = (torch.arange(nrows, device=dev) * (m // nrows) + (args.seed * 7919) % max(m // nrows, 1)) % m
+                want = full_a[rows].double() @ full_b.double()
+                got = got[rows]
+                verified_rows = nrows
+            else:
+                want = full_a.double() @ full_b.double()
+                verified_rows = m
+            if world.is_cuda:
+                torch.cuda.synchronize()
+            err = float((got.double() - want).abs().max().item())
+            limit = getattr(args, "verify_tolerance", None)
+            if limit is not None and not err <= limit * max(1.0, float(want.abs().max().item())):
+                raise RuntimeError(f"result differs from the fp64 product: max abs error {err:.3e}")
+        stats = {}
+        if mats is not None and world.is_cuda:
+            from universal_gemm_b200.parallel.exec import cached_programs
+
+            progs = cached_programs()
+            if progs:
+                stats = max((p.stats for _, p in progs), key=lambda st: st.get("tiles", 0))
         if rank != 0:
             return None
         flops = float(2.0 * m * n * k)
         tflops = [flops / d / 1e12 for d in durations]
+        peak = float(getattr(args, "peak_tflops", 0) or 0)
+        link = float(getattr(args, "link_gbs", 0) or 0)
+        roof = None
+        if peak > 0:
+            roof = flops / size / (peak * 1e12)
+            if link > 0 and stats:
+                roof = max(roof, stats.get("remote_bytes", 0) / (link * 1e9), stats.get("push_bytes", 0) / (link * 1e9))
+        med = statistics.median(durations)
         return BenchResult(
+            verified_rows=verified_rows, remote_in_bytes=stats.get("remote_bytes"), remote_out_bytes=stats.get("push_bytes"),
+            tile_variant=str(stats.get("tile_m", "")), roofline_seconds=roof,
+            roofline_fraction=(roof / med) if roof else None,
             method=args.method, m=m, n=n, k=k, a_partition=args.a_partition, b_partition=args.b_partition,
             c_partition=args.c_partition, replication_factor=args.replication_factor,
             warmup_iters=args.warmup_iters, measure_iters=args.measure_iters, world_size=size,
@@ -208,6 +245,11 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--device", choices=["cuda", "cpu"], default="cuda" if torch.cuda.is_available() else "cpu")
     p.add_argument("--b-scale", type=float, default=1.0)
     p.add_argument("--verify", action="store_true", help="compare the result with an fp64 matmul of the full matrices")
+    p.add_argument("--verify-rows", type=int, default=0, help="verify only this many sampled rows (0 = all rows)")
+    p.add_argument("--verify-tolerance", type=float, default=None,
+                   help="fail the case when the max abs error exceeds this times max(1, max |C|)")
+    p.add_argument("--peak-tflops", type=float, default=0.0, help="bf16 GEMM peak of one GPU for the roofline fields")
+    p.add_argument("--link-gbs", type=float, default=0.0, help="NVLink rate per direction per GPU for the roofline fields")
     p.add_argument("--cuda-graph", action="store_true", help="replay each stationary GEMM from a captured CUDA graph")
     args = p.parse_args(argv)
     for name in ("a_partition", "b_partition", "c_partition"):

@@ -60,7 +60,7 @@ def preset_baseline(world_size: int, full: bool) -> list[tuple[ShapeCase, Method
         [("row", "row", "row"), ("row", "column", "row"), ("column", "row", "row"), ("block", "block", "block"),
          ("block", "row", "column")]
     for shape in odd_shapes:
-        add(shape, triples, [1], ("auto",))
+        add(shape, triples, [1], ("dtensor", "auto"))
     return cases
 
 
@@ -82,6 +82,11 @@ def main() -> None:
     ap.add_argument("--device", choices=["cuda", "cpu"], default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--theoretical-tflops", type=float, default=None)
     ap.add_argument("--verify", action="store_true")
+    ap.add_argument("--verify-rows", type=int, default=0, help="verify sampled rows only (0 = every row)")
+    ap.add_argument("--verify-tolerance", type=float, default=None, help="fail a case above this relative error")
+    ap.add_argument("--peak-tflops", type=float, default=0.0, help="bf16 GEMM peak of one GPU (roofline fields)")
+    ap.add_argument("--link-gbs", type=float, default=0.0, help="NVLink GB/s per direction per GPU (roofline fields)")
+    ap.add_argument("--only-groups", default="", help="comma-separated experiment groups to keep (e.g. odd_cube,skinny)")
     ap.add_argument("--cuda-graph", action="store_true", help="replay each stationary GEMM from a captured CUDA graph")
     ap.add_argument("--max-cases", type=int, default=0)
     ap.add_argument("--only-methods", default="", help="comma-separated filter applied to the case list")
@@ -105,6 +110,9 @@ def main() -> None:
     if args.only_methods:
         keep = set(parse_csv_list(args.only_methods))
         cases = [(s, mc) for s, mc in cases if mc.method in keep]
+    if args.only_groups:
+        keep_groups = set(parse_csv_list(args.only_groups))
+        cases = [(s, mc) for s, mc in cases if s.experiment_group in keep_groups]
     if args.max_m > 0:
         cases = [(s, mc) for s, mc in cases if s.m <= args.max_m]
     if args.max_cases > 0:
@@ -118,7 +126,8 @@ def main() -> None:
             warmup_iters=args.warmup_iters, measure_iters=args.measure_iters, seed=args.seed + idx,
             theoretical_tflops=args.theoretical_tflops, dtype=args.dtype or ("bf16" if args.device == "cuda" else "fp32"),
             c_dtype=args.c_dtype, device=args.device, b_scale=1.0 / max(shape.k, 1) ** 0.5, verify=args.verify,
-            result_file="", cuda_graph=args.cuda_graph)
+            result_file="", cuda_graph=args.cuda_graph, verify_rows=args.verify_rows,
+            verify_tolerance=args.verify_tolerance, peak_tflops=args.peak_tflops, link_gbs=args.link_gbs)
         ok = torch.ones(1, device=world.device)
         try:
             rec = worker.bench_case(world, ns)

@@ -487,3 +487,83 @@ def test_gemm_kernel_c_region_on_odd_columns(offset, n, mode, tile_m):
     ref = a.float() @ b.float() + (0 if mode == "store" else big0[:, offset:offset + n])
     torch.testing.assert_close(c, ref, rtol=2e-3, atol=2e-3)
     assert torch.equal(big[:, :offset], big0[:, :offset]) and torch.equal(big[:, offset + n:], big0[:, offset + n:])
+
+
+@pytest.mark.parametrize("method", ["stationary_c", "stationary_b"])
+@pytest.mark.parametrize("triple", [("row", "column", "row"), ("column", "row", "row"), ("block", "block", "block")])
+def test_skinny_problem_splits_k_across_the_gpu(method, triple):
+    """M = 64 against a long K: a rank has a handful of output tiles, so the lowering cuts K into parts that add into
+    C atomically (all ranks zero C first when beta = 0).  Result and beta = 1 accumulation must be unchanged."""
+    from universal_gemm_b200.parallel import exec as X
+
+    m, n, k = 64, 2100, 4500
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=31, device=_dev())
+    cluster = ug.EmulatedCluster(8, _dev())
+    mats = build_cluster_matrices(cluster, full_a, full_b, full_c, triple, 1, torch.bfloat16, torch.float32)
+    X.clear_program_cache()
+    prod = full_a.bfloat16().double() @ full_b.bfloat16().double()
+    for _, _, c in mats:                                   # beta = 0: every rank clears its C, then all ranks add
+        c.local_padded.fill_(3.0)
+    progs = []
+    from universal_gemm_b200.parallel import plan as P
+    for a, b, c in mats:
+        kind = "b" if method == "stationary_b" else "c"
+        build = P.build_stationary_b_ops if kind == "b" else P.build_stationary_c_ops
+        ops = build(a.layout, b.layout, c.layout, rank=c.rank)
+        prog, needs_zero = X._program(kind, a, b, c, ops, True, 0)
+        assert needs_zero
+        progs.append((prog, c))
+    assert any(p.stats["tasks"] >= 2 and p.stats["tiles"] >= 16 for p, _ in progs), [p.stats for p, _ in progs]
+    if triple[0] != "column" and method == "stationary_b":   # A rows spread over the ranks and one B tile per rank:
+        # the 8-row tasks of a rank share their B slices and were merged into stacked ones
+        assert all(p.stats["indirect_rows"] > 0 for p, _ in progs), [p.stats for p, _ in progs]
+    from universal_gemm_b200.ops.device import DeviceState
+    st = DeviceState.get(_dev())
+    for _, c in progs:
+        c.local_padded.zero_()
+    for prog, _ in progs:
+        prog.reset_flags(st.stream())
+        prog.launch(st.stream())
+    _status_ok()
+    torch.testing.assert_close(mats[0][2].full_tensor().double(), prod, rtol=2e-3, atol=2e-3)
+    X.clear_program_cache()
+    for a, b, c in mats:                                   # beta = 1 through the public call
+        ug.matmul(a, b, c, method=method)
+    _status_ok()
+    torch.testing.assert_close(mats[0][2].full_tensor().double(), 2 * prod, rtol=2e-3, atol=2e-3)
+    X.clear_program_cache()
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 384), (300, 520, 200), (375, 1000, 1001), (64, 4099, 1024)])
+@pytest.mark.parametrize("tile_m", [128, "pair"])
+def test_gemm_kernel_fp32_operands_as_three_bf16_products(m, n, k, tile_m):
+    """fp32 A and B: the fetch warps split every element into a bf16 high and low part while staging and the
+    kernel accumulates lo x hi + hi x lo + hi x hi in fp32.  The result must be far closer to the fp64 product
+    than a single bf16 product is (and within the reference example's tolerance for fp32 results)."""
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.gemm import gemm
+
+    torch.manual_seed(m + k)
+    a = torch.randn(m, k, device=_dev())
+    b = torch.randn(k, n, device=_dev()) / k ** 0.5
+    c = torch.full((m, n), 9.0, device=_dev())
+    gemm(a, b, c, mode=native.C_STORE, tile_m=tile_m)
+    _status_ok()
+    want = a.double() @ b.double()
+    err = (c.double() - want).abs().max().item()
+    bf16_err = ((a.bfloat16().double() @ b.bfloat16().double()) - want).abs().max().item()
+    assert err < 1e-4 and err < bf16_err / 50, (err, bf16_err)
+
+
+@pytest.mark.parametrize("method", ["stationary_c", "stationary_b"])
+def test_fused_fp32_operands_emulated(method):
+    m, n, k = 301, 203, 517
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=41, device=_dev())
+    for triple in [("row", "column", "row"), ("block", "block", "block"), ("column", "row", "row")]:
+        cluster = ug.EmulatedCluster(4, _dev(), guard_bytes=4096)
+        mats = build_cluster_matrices(cluster, full_a, full_b, full_c, triple, 1, torch.float32, torch.float32)
+        run_cluster(cluster, mats, method)
+        _status_ok()
+        assert cluster.check_guards() == 12
+        want = full_c.double() + full_a.double() @ full_b.double()
+        torch.testing.assert_close(mats[0][2].full_tensor().double(), want, rtol=1e-4, atol=1e-4)

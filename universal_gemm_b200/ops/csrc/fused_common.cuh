@@ -164,6 +164,21 @@ __device__ __forceinline__ bool task_c_vec(const UgTask& t) { return (t.c_vec & 
 // Bit 1 of c_vec: the row pitch of C is a multiple of 16 bytes (and C is element-aligned), so every row of a region
 // has the same alignment phase even when the region starts on an odd column.
 __device__ __forceinline__ bool task_c_pitch_vec(const UgTask& t) { return (t.c_vec & 2) != 0; }
+// Bit 2 of c_vec: the task's output rows live in several places (a task merged from tasks of different C tiles);
+// c_ptr is then the address of a table uint64[m] with the address of every row's first column, and ldc is unused.
+// All rows share one 16-byte alignment phase (checked when the table is built).
+__device__ __forceinline__ bool task_c_rows_indirect(const UgTask& t) { return (t.c_vec & 4) != 0; }
+
+// Where the 32 rows of an epilogue warp go: rows of one region (base + r * ldc) or rows named by a table.
+struct CRows {
+  const uint64_t* tab;   // entry of the warp's first row, or nullptr
+  float* base;           // first row of the warp at the region's first column (direct), unused with a table
+  int64_t ldc;
+  int col;               // column offset added to a table entry
+  __device__ __forceinline__ float* row(int r) const {
+    return tab != nullptr ? reinterpret_cast<float*>(tab[r]) + col : base + r * ldc;
+  }
+};
 
 struct TileCoord {
   int task;
@@ -388,8 +403,8 @@ __device__ __forceinline__ void store_chunk_scalar(float* sb, const uint32_t (&v
 
 // The same transpose for a 32-column chunk of which only columns [lo, hi) are to be written (lo a multiple of 4;
 // c_base 16-byte aligned): whole 16-byte groups inside the range go out as vectors, the ragged end element by element.
-__device__ __forceinline__ void store_chunk_f32_ragged(float* sb, const uint32_t (&v)[32], int lane, float* c_base,
-                                                       int64_t ldc, int rows_valid, int mode, int lo, int hi) {
+__device__ __forceinline__ void store_chunk_f32_ragged(float* sb, const uint32_t (&v)[32], int lane, const CRows& rows,
+                                                       int col, int rows_valid, int mode, int lo, int hi) {
 #pragma unroll
   for (int j = 0; j < 8; ++j)
     *reinterpret_cast<uint4*>(sb + epi_off(lane, j)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -401,7 +416,7 @@ __device__ __forceinline__ void store_chunk_f32_ragged(float* sb, const uint32_t
       const int r = i * 4 + rsub;
       if (r < rows_valid) {
         float4 x = *reinterpret_cast<const float4*>(sb + epi_off(r, lane & 7));
-        float* g = c_base + r * ldc + cseg;
+        float* g = rows.row(r) + col + cseg;
         if (cseg + 4 <= hi) {
           float4* g4 = reinterpret_cast<float4*>(g);
           if (mode == 1) {
@@ -437,15 +452,27 @@ __device__ __forceinline__ void store_chunk_f32_ragged(float* sb, const uint32_t
 __device__ __forceinline__ void epilogue_drain_f32_shifted(uint32_t taddr, const UgTask& t, int row0, int col0,
                                                            int n_rem, int avail, float* epi_buf, int lane) {
   const int rows_valid = min(32, t.m - row0);
-  float* c_row = reinterpret_cast<float*>(t.c_ptr) + static_cast<int64_t>(row0) * t.ldc + col0;
-  const int phase = static_cast<int>((reinterpret_cast<uint64_t>(c_row) >> 2) & 3u);
+  if (rows_valid <= 0) return;
+  CRows rows;
+  if (task_c_rows_indirect(t)) {
+    rows.tab = reinterpret_cast<const uint64_t*>(t.c_ptr) + row0;
+    rows.base = nullptr;
+    rows.ldc = 0;
+    rows.col = col0;
+  } else {
+    rows.tab = nullptr;
+    rows.base = reinterpret_cast<float*>(t.c_ptr) + static_cast<int64_t>(row0) * t.ldc + col0;
+    rows.ldc = t.ldc;
+    rows.col = 0;
+  }
+  const int phase = static_cast<int>((reinterpret_cast<uint64_t>(rows.row(0)) >> 2) & 3u);
   const int head = min((4 - phase) & 3, n_rem);
   uint32_t v[32];
   if (head > 0) {
     tmem_ld_32x32(taddr, v);
     tmem_ld_wait();
     if (lane < rows_valid) {
-      float* g = c_row + lane * t.ldc;
+      float* g = rows.row(lane);
 #pragma unroll
       for (int j = 0; j < 3; ++j) {
         if (j < head) {
@@ -461,7 +488,7 @@ __device__ __forceinline__ void epilogue_drain_f32_shifted(uint32_t taddr, const
   for (; c < n_rem && c + 32 <= avail; c += 32) {
     tmem_ld_32x32(taddr + c, v);
     tmem_ld_wait();
-    store_chunk_f32_ragged(epi_buf, v, lane, c_row + c, t.ldc, rows_valid, t.c_mode, 0, min(32, n_rem - c));
+    store_chunk_f32_ragged(epi_buf, v, lane, rows, c, rows_valid, t.c_mode, 0, min(32, n_rem - c));
   }
   if (c < n_rem) {
     // Fewer than 32 columns are left and a chunk on this boundary would read past the readable TMEM columns: move it
@@ -473,14 +500,14 @@ __device__ __forceinline__ void epilogue_drain_f32_shifted(uint32_t taddr, const
     if (lo < hi) {
       tmem_ld_32x32(taddr + start, v);
       tmem_ld_wait();
-      store_chunk_f32_ragged(epi_buf, v, lane, c_row + start, t.ldc, rows_valid, t.c_mode, lo, hi);
+      store_chunk_f32_ragged(epi_buf, v, lane, rows, start, rows_valid, t.c_mode, lo, hi);
     }
     const int rem = n_rem - min(start + 32, n_rem);
     if (rem > 0) {
       tmem_ld_32x32(taddr + n_rem - 32, v);
       tmem_ld_wait();
       if (lane < rows_valid) {
-        float* g = c_row + lane * t.ldc + n_rem - 32;
+        float* g = rows.row(lane) + n_rem - 32;
 #pragma unroll
         for (int j = 29; j < 32; ++j) {
           if (j >= 32 - rem) {
@@ -496,6 +523,76 @@ __device__ __forceinline__ void epilogue_drain_f32_shifted(uint32_t taddr, const
 }
 
 // ---------------------------------------------------------------- fetch warps
+__device__ __forceinline__ float4 ld_stream_f4(const void* p) {
+  const uint4 u = ld_stream_v4(p);
+  return make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+}
+__device__ __forceinline__ float ld_stream_f1(const void* p) {
+  float v;
+  asm volatile("ld.global.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+// High and low bf16 parts of two fp32 values: hi = bf16(x), lo = bf16(x - hi), packed as bf16x2.
+__device__ __forceinline__ void split_bf16x2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+  const __nv_bfloat162 hp = __halves2bfloat162(h0, h1);
+  const __nv_bfloat162 lp = __floats2bfloat162_rn(x0 - __bfloat162float(h0), x1 - __bfloat162float(h1));
+  hi = *reinterpret_cast<const uint32_t*>(&hp);
+  lo = *reinterpret_cast<const uint32_t*>(&lp);
+}
+
+// Copy an fp32 piece (possibly from a peer) into two bf16 buffers: the high parts at pc.dst, the low parts
+// (pc.mode >> 8) KiB further on.  A 16-byte destination vector holds eight elements, i.e. 32 source bytes.
+// `aligned`: source rows start on 16-byte boundaries (two vector loads per destination vector), else 4-byte loads.
+// Elements past the end of a row are written as zeros.
+__device__ __forceinline__ void copy_piece_split_f32(const UgPiece& pc, int lane, int vec_per_row, uint32_t nvec,
+                                                     bool aligned) {
+  const char* src = reinterpret_cast<const char*>(pc.src);
+  char* dst = reinterpret_cast<char*>(pc.dst);
+  const int64_t low = static_cast<int64_t>(static_cast<uint32_t>(pc.mode) >> 8) << 10;
+  const uint32_t vpr = static_cast<uint32_t>(vec_per_row);
+  const int row_elems = pc.row_bytes >> 1;
+  constexpr uint32_t U = 4;                       // destination vectors per lane and batch: 8 x 16 B loads in flight
+  for (uint32_t base = 0; base < nvec; base += 32u * U) {
+    float f[U][8];
+#pragma unroll
+    for (uint32_t u = 0; u < U; ++u) {
+      const uint32_t idx = min(base + u * 32u + static_cast<uint32_t>(lane), nvec - 1u);
+      const uint32_t r = idx / vpr, c = idx - r * vpr;
+      const char* sp = src + static_cast<int64_t>(r) * pc.src_ld + (static_cast<int64_t>(c) << 5);
+      const int valid = row_elems - static_cast<int>(c << 3);          // elements of this vector inside the row
+      if (aligned) {
+        const float4 a = ld_stream_f4(sp);
+        const float4 b = valid > 4 ? ld_stream_f4(sp + 16) : make_float4(0.f, 0.f, 0.f, 0.f);
+        f[u][0] = a.x; f[u][1] = a.y; f[u][2] = a.z; f[u][3] = a.w;
+        f[u][4] = b.x; f[u][5] = b.y; f[u][6] = b.z; f[u][7] = b.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[u][e] = e < valid ? ld_stream_f1(sp + 4 * e) : 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (e >= valid) f[u][e] = 0.f;
+    }
+    asm volatile("" ::: "memory");
+#pragma unroll
+    for (uint32_t u = 0; u < U; ++u) {
+      const uint32_t idx = base + u * 32u + static_cast<uint32_t>(lane);
+      if (idx < nvec) {
+        const uint32_t r = idx / vpr, c = idx - r * vpr;
+        uint4 hi, lo;
+        split_bf16x2(f[u][0], f[u][1], hi.x, lo.x);
+        split_bf16x2(f[u][2], f[u][3], hi.y, lo.y);
+        split_bf16x2(f[u][4], f[u][5], hi.z, lo.z);
+        split_bf16x2(f[u][6], f[u][7], hi.w, lo.w);
+        char* dp = dst + static_cast<int64_t>(r) * pc.dst_ld + (static_cast<int64_t>(c) << 4);
+        *reinterpret_cast<uint4*>(dp) = hi;
+        *reinterpret_cast<uint4*>(dp + low) = lo;
+      }
+    }
+  }
+}
+
 // Copy one piece with the 32 lanes of a warp.  mode 0: 16-byte vectors, sixteen in
 // flight per lane.  mode 1: the source is only 2-byte aligned; every 16-byte
 // destination vector is gathered from eight 2-byte loads.
@@ -505,7 +602,12 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
   const int64_t total = static_cast<int64_t>(pc.rows) * vec_per_row;
   const char* src = reinterpret_cast<const char*>(pc.src);
   char* dst = reinterpret_cast<char*>(pc.dst);
-  if (pc.mode == 0) {
+  const int mode = pc.mode & 0xff;
+  if (mode >= 2) {
+    copy_piece_split_f32(pc, lane, vec_per_row, static_cast<uint32_t>(total), mode == 2);
+    return;
+  }
+  if (mode == 0) {
     // The piece is walked as one flat sequence of 16-byte vectors (row after row); a warp takes 32 x U consecutive
     // vectors per batch, whatever the piece's shape (one 24 KiB row or 128 rows of 256 bytes).  The batch is
     // straight-line code: U unconditional loads (lanes past the end re-read the last vector), a compiler barrier,
@@ -559,7 +661,8 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
 __device__ __forceinline__ void epilogue_drain(uint32_t taddr, const UgTask& t, int row0, int col0, int n_rem,
                                                int avail, float* epi_buf, int lane) {
   const int rows_valid = min(32, t.m - row0);               // <= 0 when the warp is past the region
-  if (t.c_dtype == 0 && task_c_pitch_vec(t) && !(task_c_vec(t) && (n_rem & 31) == 0 && (col0 & 3) == 0)) {
+  if (t.c_dtype == 0 && task_c_pitch_vec(t) &&
+      (task_c_rows_indirect(t) || !(task_c_vec(t) && (n_rem & 31) == 0 && (col0 & 3) == 0))) {
     epilogue_drain_f32_shifted(taddr, t, row0, col0, n_rem, avail, epi_buf, lane);
     return;
   }

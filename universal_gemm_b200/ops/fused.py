@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Callable, Sequence
 
 import numpy as np
@@ -61,10 +61,14 @@ class OperandSlice:
     cols: int
     remote: bool = False
     elem_bytes: int = 2
+    # fp32 operands run as three bf16 products (a = hi + lo with hi = bf16(a), lo = bf16(a - hi);
+    # A @ B ~ Ahi Bhi + Ahi Blo + Alo Bhi): split = 1 names the high part of an fp32 slice, 2 the low part.
+    # Such a slice has elem_bytes = 4 and is always staged; the fetch warps convert while they copy.
+    split: int = 0
 
     def tma_ok(self) -> bool:
-        return (not self.remote) and self.base % 16 == 0 and (self.ld * self.elem_bytes) % 16 == 0 \
-            and (self.col0 * self.elem_bytes) % 16 == 0
+        return self.split == 0 and (not self.remote) and self.base % 16 == 0 \
+            and (self.ld * self.elem_bytes) % 16 == 0 and (self.col0 * self.elem_bytes) % 16 == 0
 
     def vector_ok(self) -> bool:
         return self.base % 16 == 0 and (self.ld * self.elem_bytes) % 16 == 0 \
@@ -72,6 +76,69 @@ class OperandSlice:
 
     def address(self, r: int = 0, c: int = 0) -> int:
         return self.base + ((self.row0 + r) * self.ld + self.col0 + c) * self.elem_bytes
+
+    # the three operations below exist on StackedSlice too
+    def row_parts(self) -> list[tuple["OperandSlice", int]]:
+        """(contiguous source, first row of it in this slice) pairs."""
+        return [(self, 0)]
+
+    def with_cols(self, first: int, count: int) -> "OperandSlice":
+        return replace(self, col0=self.col0 + first, cols=count)
+
+    def with_split(self, split: int) -> "OperandSlice":
+        return replace(self, split=split)
+
+    def remote_bytes(self) -> int:
+        return self.rows * self.cols * self.elem_bytes if self.remote else 0
+
+
+@dataclass(frozen=True)
+class StackedSlice:
+    """Row slices of several tiles (same columns, same dtype) stacked into one A operand.  It exists only in the
+    staging buffer: the fetch warps copy every part, local ones too, to its place in the stack.  Used to merge the
+    tasks of a skinny problem whose A is partitioned by rows (M = 64 on 8 ranks gives tiles of 8 rows; one task per
+    tile would run a full 128-row tensor tile, and stream all of B, for 8 rows of output)."""
+
+    parts: tuple[OperandSlice, ...]
+
+    @property
+    def rows(self) -> int:
+        return sum(p.rows for p in self.parts)
+
+    @property
+    def cols(self) -> int:
+        return self.parts[0].cols
+
+    @property
+    def elem_bytes(self) -> int:
+        return self.parts[0].elem_bytes
+
+    @property
+    def split(self) -> int:
+        return self.parts[0].split
+
+    @property
+    def remote(self) -> bool:
+        return any(p.remote for p in self.parts)
+
+    def tma_ok(self) -> bool:
+        return False
+
+    def row_parts(self) -> list[tuple[OperandSlice, int]]:
+        out, off = [], 0
+        for p in self.parts:
+            out.append((p, off))
+            off += p.rows
+        return out
+
+    def with_cols(self, first: int, count: int) -> "StackedSlice":
+        return StackedSlice(tuple(p.with_cols(first, count) for p in self.parts))
+
+    def with_split(self, split: int) -> "StackedSlice":
+        return StackedSlice(tuple(p.with_split(split) for p in self.parts))
+
+    def remote_bytes(self) -> int:
+        return sum(p.remote_bytes() for p in self.parts)
 
 
 @dataclass
@@ -85,6 +152,9 @@ class TaskSpec:
     segments: list[tuple[OperandSlice, OperandSlice]] = field(default_factory=list)
     c_remote: bool = False      # C lives in a peer's memory (the epilogue pushes over NVLink)
     tile_n: int = BN            # columns per output tile (128 for tasks moved into the last, partial wave)
+    # Output rows that live in several places (a task merged from tasks of different C tiles): (address of the first
+    # row's first column, row pitch in elements, rows) per part, in row order; c_ptr / ldc are then unused.
+    c_rows: tuple[tuple[int, int, int], ...] | None = None
 
 
 @dataclass
@@ -96,6 +166,8 @@ class _Staged:
     flag_base: int
     num_chunks: int
     map_index: int = -1
+    pieces_of: "_Staged | None" = None   # low part of a split fp32 slice: the high part's pieces fill this buffer too
+    low: "_Staged | None" = None         # high part of a split fp32 slice: where the low part goes
 
 
 class FusedProgram:
@@ -159,8 +231,10 @@ class FusedProgram:
 
 class FusedProgramBuilder:
     def __init__(self, device: torch.device, *, num_sms: int | None = None, timeout_ns: int = 4_000_000_000,
-                 range_check: Callable[[int, int, str], None] | None = None, tile_m: int | None = None):
+                 range_check: Callable[[int, int, str], None] | None = None, tile_m: int | None = None,
+                 split_k: bool = False):
         self.device = torch.device(device)
+        self.split_k = bool(split_k)
         if num_sms is None:
             num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.num_sms = int(num_sms)
@@ -173,6 +247,46 @@ class FusedProgramBuilder:
             raise ValueError('tile_m must be 128, 256, "pair" or "pair512"')
         self.tile_m = tile_m
         self.tasks: list[TaskSpec] = []
+
+    def merge_row_tasks(self, max_rows: int = 256) -> int:
+        """Merge tasks that multiply different rows of A with the same B slices (and write equally wide regions of an
+        fp32 C) into one task whose A is the stack of their row slices and whose output rows go to their several
+        places.  Only tasks of fewer than 128 rows are merged, up to ``max_rows`` rows per merged task: this is for
+        skinny problems, where every such task would otherwise occupy a whole tensor tile and stream B again.
+        Returns the number of tasks saved."""
+        groups: dict[tuple, list[TaskSpec]] = {}
+        order: list[tuple] = []
+        for t in self.tasks:
+            key = None
+            if t.m < 128 and t.c_dtype == native.DT_F32 and t.c_rows is None and (t.ldc * 4) % 16 == 0 and \
+                    t.c_ptr % 4 == 0 and all(isinstance(a, OperandSlice) for a, _ in t.segments):
+                key = (t.n, t.c_mode, t.tile_n, (t.c_ptr % 16, (t.ldc * 4) % 16),
+                       tuple((b, a.col0, a.cols, a.elem_bytes, a.split) for a, b in t.segments))
+            else:
+                key = ("single", id(t))
+            if key not in groups:
+                groups[key] = []
+                order.append(key)
+            groups[key].append(t)
+        merged: list[TaskSpec] = []
+        for key in order:
+            bucket = groups[key]
+            while bucket:
+                take, rows = [], 0
+                while bucket and (not take or rows + bucket[0].m <= max_rows):
+                    rows += bucket[0].m
+                    take.append(bucket.pop(0))
+                if len(take) == 1:
+                    merged.append(take[0])
+                    continue
+                segs = [(StackedSlice(tuple(t.segments[i][0] for t in take)), take[0].segments[i][1])
+                        for i in range(len(take[0].segments))]
+                merged.append(TaskSpec(c_ptr=take[0].c_ptr, ldc=take[0].ldc, m=rows, n=take[0].n, c_mode=take[0].c_mode,
+                                       c_dtype=take[0].c_dtype, segments=segs, c_remote=any(t.c_remote for t in take),
+                                       tile_n=take[0].tile_n, c_rows=tuple((t.c_ptr, t.ldc, t.m) for t in take)))
+        saved = len(self.tasks) - len(merged)
+        self.tasks = merged
+        return saved
 
     def add_task(self, task: TaskSpec) -> None:
         if task.m <= 0 or task.n <= 0 or not task.segments:
@@ -210,7 +324,11 @@ class FusedProgramBuilder:
             return None
         per_worker = [0.0] * workers
         tile = 0
-        for t in self.tasks:
+        tasks = self.tasks
+        if self.split_k and os.environ.get("UGEMM_SPLIT_K", "1") != "0":
+            tasks = self._split_k([t if v["cols"] == BN else self._with_tile_n(t, v["cols"]) for t in tasks],
+                                  v["rows"], workers)
+        for t in tasks:
             kblocks = sum((a.cols + BK - 1) // BK for a, _ in t.segments)
             tiles = ((t.m + v["rows"] - 1) // v["rows"]) * ((t.n + v["cols"] - 1) // v["cols"])
             main = kblocks * v["kb_us"]
@@ -237,11 +355,11 @@ class FusedProgramBuilder:
         workers = (self.num_sms // 2) if pair else self.num_sms
         tasks = self.tasks
         if wide:
-            from dataclasses import replace
-
             tasks = [replace(t, tile_n=2 * BN) if t.tile_n == BN else t for t in tasks]
         if os.environ.get("UGEMM_TAIL_SPLIT", "1") != "0":
             tasks = self._split_tail(tasks, BM, workers, 2 * BN if wide else BN)
+        if self.split_k and os.environ.get("UGEMM_SPLIT_K", "1") != "0":
+            tasks = self._split_k(tasks, BM, workers)
         map_keys: dict[tuple, int] = {}
         map_specs: list[tuple] = []
 
@@ -264,18 +382,28 @@ class FusedProgramBuilder:
             st = staged.get(key)
             if st is not None:
                 return st
+            if src.split == 2:                 # the low part lives beside its high part and shares its counters
+                stage(kind, src.with_split(1))
+                return staged[key]
             ld = _round_up(src.cols, 64)
-            nbytes = _round_up(src.rows * ld * src.elem_bytes, 1024)
+            nbytes = _round_up(src.rows * ld * 2, 1024)        # staged data is always bf16
             chunks = (src.rows + BM - 1) // BM if kind == "a" else (src.cols + BN - 1) // BN
             st = _Staged(kind=kind, src=src, offset=staging_bytes, ld=ld, flag_base=num_flags, num_chunks=chunks)
             staging_bytes += nbytes
             num_flags += chunks
             staged[key] = st
+            if src.split == 1:
+                low = _Staged(kind=kind, src=src.with_split(2), offset=staging_bytes, ld=ld,
+                              flag_base=st.flag_base, num_chunks=chunks, pieces_of=st)
+                staging_bytes += nbytes
+                st.low = low
+                staged[(kind, low.src)] = low
             return st
 
         # Pass 1: decide direct vs staged per operand and lay out tasks / segments.
         seg_rows = []
         task_rows = []
+        row_table: list[int] = []      # per-row C addresses of tasks whose output rows live in several places
         tile_begin = 0
         seg_sources: list[tuple[_Staged | None, _Staged | None]] = []
         for task in tasks:
@@ -291,7 +419,7 @@ class FusedProgramBuilder:
                     sa = None
                 else:
                     sa = stage("a", a)
-                    sa.map_index = add_map(sa.offset, True, a.cols, a.rows, sa.ld * a.elem_bytes, (BK, a_box_rows))
+                    sa.map_index = add_map(sa.offset, True, a.cols, a.rows, sa.ld * 2, (BK, a_box_rows))
                     row["a_map"], row["a_row0"], row["a_col0"], row["a_flag"] = sa.map_index, 0, 0, sa.flag_base
                 if b.tma_ok():
                     row["b_map"] = add_map(b.base, False, b.col0 + b.cols, b.row0 + b.rows, b.ld * b.elem_bytes, (64, BK))
@@ -299,7 +427,7 @@ class FusedProgramBuilder:
                     sb = None
                 else:
                     sb = stage("b", b)
-                    sb.map_index = add_map(sb.offset, True, b.cols, b.rows, sb.ld * b.elem_bytes, (64, BK))
+                    sb.map_index = add_map(sb.offset, True, b.cols, b.rows, sb.ld * 2, (64, BK))
                     row["b_map"], row["b_row0"], row["b_col0"], row["b_flag"] = sb.map_index, 0, 0, sb.flag_base
                 seg_rows.append(row)
                 seg_sources.append((sa, sb))
@@ -308,6 +436,18 @@ class FusedProgramBuilder:
             c_vec = int(task.c_ptr % 16 == 0 and (task.ldc * c_elem) % 16 == 0)
             if task.c_ptr % c_elem == 0 and (task.ldc * c_elem) % 16 == 0:
                 c_vec |= 2          # rows share one alignment phase: vector stores from the next 16-byte boundary on
+            row_tab_at = -1
+            if task.c_rows is not None:
+                # rows in several places: the kernel reads each row's address from a table (bit 2 of c_vec); all
+                # rows must share one 16-byte phase, which the vector stores of the epilogue rely on
+                if task.c_dtype != native.DT_F32 or sum(r for _, _, r in task.c_rows) != task.m:
+                    raise ValueError("a task with several output parts needs fp32 C and parts that add up to m")
+                addrs = [ptr + i * ld * c_elem for ptr, ld, rows in task.c_rows for i in range(rows)]
+                if len({x % 16 for x in addrs}) != 1 or addrs[0] % c_elem:
+                    raise ValueError("the output rows of a merged task differ in alignment")
+                c_vec = 2 | 4
+                row_tab_at = len(row_table)
+                row_table.extend(addrs)
             if task.tile_n != BN:
                 c_vec |= task.tile_n << 16
             band = 2048 // BM
@@ -317,6 +457,7 @@ class FusedProgramBuilder:
                                   n_tiles=n_tiles, kblocks=kblocks, c_mode=task.c_mode, c_dtype=task.c_dtype,
                                   c_vec=c_vec, group_m=group_m))
             task_rows[-1]["tile_n"] = task.tile_n
+            task_rows[-1]["row_tab_at"] = row_tab_at
             tile_begin += m_tiles * n_tiles
         total_tiles = tile_begin
         if len(map_specs) > 4096:
@@ -339,9 +480,17 @@ class FusedProgramBuilder:
         pieces_by_chunk: dict[tuple[int, int], list[dict]] = {}
         flag_need = np.zeros(max(num_flags, 1), dtype=np.int32)
         for st in staged.values():
+            if st.pieces_of is not None:
+                continue
             src = st.src
             eb = src.elem_bytes
-            mode = 0 if src.vector_ok() else 1
+            dist_kib = 0
+            if src.split:
+                # convert while copying: mode 2 (16-byte loads) / 3 (4-byte loads); the distance to the low part's
+                # buffer travels in the upper bits of the mode word, in KiB
+                dist_kib = (st.low.offset - st.offset) >> 10
+                if (st.low.offset - st.offset) % 1024 or dist_kib >= 1 << 22:
+                    raise ValueError("staging area too large for split fp32 operands")
             for c in range(st.num_chunks):
                 plist = []
                 if st.kind == "a":
@@ -350,16 +499,24 @@ class FusedProgramBuilder:
                 else:
                     r0, r1 = 0, src.rows
                     c0, c1 = c * BN, min(src.cols, (c + 1) * BN)
-                row_bytes = (c1 - c0) * eb
+                row_bytes = (c1 - c0) * 2                      # payload per row of the (bf16) destination
                 rpp = max(1, _PIECE_BYTES // max(row_bytes, 1))
-                for r in range(r0, r1, rpp):
-                    rows = min(rpp, r1 - r)
-                    plist.append(dict(src=src.address(r, c0), dst=staging_base + st.offset + (r * st.ld + c0) * eb,
-                                      src_ld=src.ld * eb, dst_ld=st.ld * eb, rows=rows, row_bytes=row_bytes,
-                                      flag=st.flag_base + c, mode=mode))
-                    if self.range_check is not None:
-                        span = (rows - 1) * src.ld * eb + (_round_up(row_bytes, 16) if mode == 0 else row_bytes)
-                        self.range_check(src.address(r, c0), span, "staged source")
+                for part, first in src.row_parts():            # one contiguous source at a time
+                    p0, p1 = max(r0, first), min(r1, first + part.rows)
+                    if part.split:
+                        mode = (2 if part.vector_ok() else 3) | (dist_kib << 8)
+                    else:
+                        mode = 0 if part.vector_ok() else 1
+                    for r in range(p0, p1, rpp):
+                        rows = min(rpp, p1 - r)
+                        plist.append(dict(src=part.address(r - first, c0),
+                                          dst=staging_base + st.offset + (r * st.ld + c0) * 2,
+                                          src_ld=part.ld * eb, dst_ld=st.ld * 2, rows=rows, row_bytes=row_bytes,
+                                          flag=st.flag_base + c, mode=mode))
+                        if self.range_check is not None:
+                            src_row = (c1 - c0) * eb
+                            span = (rows - 1) * part.ld * eb + (_round_up(src_row, 16) if mode & 0xff in (0, 2) else src_row)
+                            self.range_check(part.address(r - first, c0), span, "staged source")
                 pieces_by_chunk[(id(st), c)] = plist
                 flag_need[st.flag_base + c] = len(plist)
 
@@ -384,7 +541,7 @@ class FusedProgramBuilder:
                         for st, ci in wanted:
                             if st is None:
                                 continue
-                            key = (id(st), ci)
+                            key = (id(st.pieces_of or st), ci)
                             if key not in emitted:
                                 emitted.add(key)
                                 ordered.extend(pieces_by_chunk[key])
@@ -400,7 +557,7 @@ class FusedProgramBuilder:
         task_arr = np.zeros(max(len(task_rows), 1), dtype=native.TASK_DTYPE)
         for i, row in enumerate(task_rows):
             for k, v in row.items():
-                if k != "tile_n":
+                if k not in ("tile_n", "row_tab_at"):
                     task_arr[i][k] = v
         piece_arr = np.zeros(max(len(ordered), 1), dtype=native.PIECE_DTYPE)
         for i, row in enumerate(ordered):
@@ -416,13 +573,21 @@ class FusedProgramBuilder:
         def pad(b: bytes, align: int = 256) -> bytes:
             return b + bytes((-len(b)) % align)
 
-        sections = [pad(bytes(maps_blob)), pad(task_arr.tobytes()), pad(seg_arr.tobytes()), pad(piece_arr.tobytes()),
-                    pad(flag_need.tobytes()), pad(bytes(4 * (num_flags + 1))), pad(bytes(8))]
-        offsets = np.cumsum([0] + [len(s) for s in sections])
-        blob = np.frombuffer(b"".join(sections), dtype=np.uint8).copy()
-        tables = torch.empty(len(blob) + 256, dtype=torch.uint8, device=dev)
+        row_tab_arr = np.asarray(row_table or [0], dtype=np.uint64)
+        lengths = [len(pad(bytes(x))) for x in (maps_blob, task_arr.tobytes(), seg_arr.tobytes(), piece_arr.tobytes(),
+                                                flag_need.tobytes(), bytes(4 * (num_flags + 1)), bytes(8),
+                                                row_tab_arr.tobytes())]
+        offsets = np.cumsum([0] + lengths)
+        tables = torch.empty(int(offsets[-1]) + 256, dtype=torch.uint8, device=dev)
         base = _round_up(tables.data_ptr(), 256)
         shift = base - tables.data_ptr()
+        for i, row in enumerate(task_rows):          # tasks with a row table point at their part of it
+            if row["row_tab_at"] >= 0:
+                task_arr[i]["c_ptr"] = base + int(offsets[7]) + 8 * row["row_tab_at"]
+                task_arr[i]["ldc"] = 0
+        sections = [pad(bytes(maps_blob)), pad(task_arr.tobytes()), pad(seg_arr.tobytes()), pad(piece_arr.tobytes()),
+                    pad(flag_need.tobytes()), pad(bytes(4 * (num_flags + 1))), pad(bytes(8)), pad(row_tab_arr.tobytes())]
+        blob = np.frombuffer(b"".join(sections), dtype=np.uint8).copy()
         tables[shift:shift + len(blob)].copy_(torch.from_numpy(blob))
 
         params = native.FusedParams()
@@ -453,9 +618,11 @@ class FusedProgramBuilder:
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
                      pieces=len(ordered), staged_bytes=staging_bytes, tile_m=variant if pair else BM,
+                     indirect_rows=len(row_table),
+                     push_bytes=sum(t.m * t.n * (4 if t.c_dtype == native.DT_F32 else 2) for t in tasks if t.c_remote),
                      model_us=round(self.model_us(variant) or 0.0, 1),
-                     remote_bytes=sum(st.src.rows * st.src.cols * st.src.elem_bytes for st in staged.values()
-                                      if st.src.remote), grid=grid)
+                     remote_bytes=sum(st.src.remote_bytes() for st in staged.values() if st.pieces_of is None),
+                     grid=grid)
         return FusedProgram(device=dev, tables=tables, staging=staging, params=params, grid=grid,
                             clear_ptr=params.flags if staged else 0, num_clear=(num_flags + 1) if staged else 0,
                             stats=stats)
@@ -497,14 +664,54 @@ class FusedProgramBuilder:
         return out
 
     @staticmethod
+    def _with_tile_n(t: TaskSpec, tile_n: int) -> TaskSpec:
+        return replace(t, tile_n=tile_n) if t.tile_n == BN else t
+
+    @staticmethod
+    def _split_k(tasks: list[TaskSpec], bm: int, workers: int) -> list[TaskSpec]:
+        """Cut the K range of atomically accumulating tasks into several tasks when the plan has far fewer output
+        tiles than workers (skinny GEMMs: M = 64 against N = K = 16383 gives a rank 8 tiles, each streaming all of
+        B's rows through one SM).  Every part adds its partial product into C with ``red.add``, so the whole GPU
+        streams B; the parts are whole K blocks, which keeps every slice's TMA alignment."""
+        counts = [((t.m + bm - 1) // bm) * ((t.n + t.tile_n - 1) // t.tile_n) for t in tasks]
+        total = sum(counts)
+        if total == 0 or total > workers:
+            return list(tasks)
+        target = workers // total
+        if target < 2:
+            return list(tasks)
+        out: list[TaskSpec] = []
+        for t in tasks:
+            kblocks = sum((a.cols + BK - 1) // BK for a, _ in t.segments)
+            parts = min(target, kblocks // 4)
+            if t.c_mode != native.C_ATOMIC or parts < 2:
+                out.append(t)
+                continue
+            per = (kblocks + parts - 1) // parts            # K blocks per part
+            cur: list[tuple[OperandSlice, OperandSlice]] = []
+            room = per
+            for a, b in t.segments:
+                done = 0
+                while done < a.cols:
+                    take = min(a.cols - done, room * BK)
+                    cur.append((a.with_cols(done, take), replace(b, row0=b.row0 + done, rows=take)))
+                    done += take
+                    room -= (take + BK - 1) // BK
+                    if room <= 0:
+                        out.append(replace(t, segments=cur))
+                        cur, room = [], per
+            if cur:
+                out.append(replace(t, segments=cur))
+        return out
+
+    @staticmethod
     def _columns(t: TaskSpec, c0: int, c1: int, tile_n: int) -> TaskSpec:
         """The sub-task of ``t`` that covers output columns ``[c0, c1)``."""
-        from dataclasses import replace
-
         elem = 4 if t.c_dtype == native.DT_F32 else 2
         segs = [(a, replace(b, col0=b.col0 + c0, cols=c1 - c0)) for a, b in t.segments]
+        c_rows = None if t.c_rows is None else tuple((ptr + c0 * elem, ld, rows) for ptr, ld, rows in t.c_rows)
         return TaskSpec(c_ptr=t.c_ptr + c0 * elem, ldc=t.ldc, m=t.m, n=c1 - c0, c_mode=t.c_mode, c_dtype=t.c_dtype,
-                        segments=segs, c_remote=t.c_remote, tile_n=tile_n)
+                        segments=segs, c_remote=t.c_remote, tile_n=tile_n, c_rows=c_rows)
 
     @staticmethod
     def _tile_coords(task_rows: Sequence[dict]) -> list[tuple[int, int, int]]:

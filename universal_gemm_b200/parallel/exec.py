@@ -2,7 +2,7 @@
 
 Two executors:
 
-* **fused** (GPU, bf16 operands): the plan is grouped into output regions, lowered
+* **fused** (GPU, bf16 operands, or fp32 operands as three bf16 products): the plan is grouped into output regions, lowered
   once into the device tables of the persistent tcgen05 kernel (cached per matrix
   triple) and every call is ``signal barrier -> fused kernel -> signal barrier`` on
   the current stream.  Remote operand slices are pulled by the kernel's fetch
@@ -11,7 +11,7 @@ Two executors:
 * **tilewise** (any device / dtype): one ``get_tile`` + matmul + ``accumulate_tile``
   per op, the structure of the reference's executors
   (stationary_c_plan.py:295-355, stationary_b_plan.py:267-337).  It is the CPU
-  path and the fp32 path.
+  path (and the path of dtype combinations the kernel does not take).
 
 Signatures follow the reference's ``execute_stationary_{b,c}`` family
 (stationary_c_plan.py:526-581, stationary_b_plan.py:567-623); arguments that tuned
@@ -63,8 +63,9 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
     from ..ops.device import DeviceState, torch_dtype_code
     from ..ops.fused import FusedProgramBuilder, OperandSlice, TaskSpec
 
-    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
-        raise TypeError("the fused executor needs bfloat16 A and B")
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("the fused executor needs A and B of one dtype, bfloat16 or float32")
+    split_f32 = a.dtype == torch.float32      # fp32 operands: three bf16 products per op (hi x hi + hi x lo + lo x hi)
     state = DeviceState.get(c.device)
     me = c.rank
     rep_c = T.replication_factor(c.layout)
@@ -76,6 +77,14 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
     single_writer = ((kind == "c" and rep_c == 1) or (kind == "b" and T.grid_shape(b.layout)[0] == 1)) \
         and not (rep_c > 1 and not fuse_replica_reduce)
     needs_zero = beta == 0 and not single_writer
+    # Skinny problems (few output tiles per rank, long K): every rank cuts K into parts that add into C atomically,
+    # so that all SMs stream the operands.  Decided from the global shape alone, hence the same on every rank: all
+    # of them then treat C as a multi-writer matrix (zeroed before the entry barrier when beta = 0).
+    tiles_per_rank = -(-c.shape[0] // 256) * -(-c.shape[1] // 256) / max(c.world.size, 1)
+    split_k = (c.dtype == torch.float32 and 4 * tiles_per_rank <= state.num_sms and a.shape[1] >= 32 * 64)
+    if split_k:
+        single_writer = False
+        needs_zero = beta == 0
 
     buffers = (a.buffer, b.buffer, c.buffer)
 
@@ -85,7 +94,7 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
 
     builder = FusedProgramBuilder(c.device, num_sms=state.num_sms,
                                   timeout_ns=getattr(c.world, "timeout_ns", 4_000_000_000),
-                                  range_check=check if range_check else None)
+                                  range_check=check if range_check else None, split_k=split_k)
     for region in P.group_ops(ops):
         c_owner = _owner(c, region.c_idx, replica=0 if push_to_origin else None)
         sl = region.c_slice
@@ -96,7 +105,7 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
         if kind == "c" and not push_to_origin:
             if c_owner != me:
                 raise RuntimeError(f"Stationary-C expects local c_idx={region.c_idx}, owner={c_owner}, rank={me}")
-            mode = native.C_ADD
+            mode = native.C_ATOMIC if split_k else native.C_ADD
         else:
             mode = native.C_ATOMIC
         if beta == 0 and single_writer:
@@ -107,12 +116,22 @@ def lower_plan(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
             if kind == "b" and bo != me:
                 raise RuntimeError(f"Stationary-B expects local b_idx={op.b_idx}, owner={bo}, rank={me}")
             sa = OperandSlice(base=a.tile_ptr(ao), ld=a.ld, row0=op.a_slice.rows.start, col0=op.a_slice.cols.start,
-                              rows=op.a_slice.shape[0], cols=op.a_slice.shape[1], remote=ao != me)
+                              rows=op.a_slice.shape[0], cols=op.a_slice.shape[1], remote=ao != me,
+                              elem_bytes=a.itemsize)
             sb = OperandSlice(base=b.tile_ptr(bo), ld=b.ld, row0=op.b_slice.rows.start, col0=op.b_slice.cols.start,
-                              rows=op.b_slice.shape[0], cols=op.b_slice.shape[1], remote=bo != me)
-            segs.append((sa, sb))
+                              rows=op.b_slice.shape[0], cols=op.b_slice.shape[1], remote=bo != me,
+                              elem_bytes=b.itemsize)
+            if split_f32:
+                from dataclasses import replace
+
+                a_hi, a_lo, b_hi, b_lo = replace(sa, split=1), replace(sa, split=2), replace(sb, split=1), replace(sb, split=2)
+                segs += [(a_lo, b_hi), (a_hi, b_lo), (a_hi, b_hi)]      # small terms first
+            else:
+                segs.append((sa, sb))
         builder.add_task(TaskSpec(c_ptr=c_ptr, ldc=c.ld, m=m, n=n, c_mode=mode, c_dtype=torch_dtype_code(c.dtype),
                                   segments=segs, c_remote=c_owner != me))
+    if split_k:
+        builder.merge_row_tasks()      # skinny problems: tasks of a few rows each that share their B slices become one
     return builder.build(state.status_ptr), needs_zero
 
 
@@ -137,8 +156,13 @@ def cached_programs() -> list:
 
 
 def _can_fuse(a: DistMatrix, b: DistMatrix, c: DistMatrix) -> bool:
-    return (c.world.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
-            and c.dtype in (torch.float32, torch.bfloat16))
+    if not c.world.is_cuda:
+        return False
+    if a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16:
+        return c.dtype in (torch.float32, torch.bfloat16)
+    # fp32 operands (the reference's benchmark dtype, benchmark/matmul_bench_worker.py:163-165) run through the
+    # same kernel as three bf16 products with fp32 accumulation; C stays fp32
+    return a.dtype == torch.float32 and b.dtype == torch.float32 and c.dtype == torch.float32
 
 
 # ----------------------------------------------------------------------------- fused executor
@@ -229,7 +253,7 @@ def _execute(kind: str, a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp] | None
         executor = "fused" if _can_fuse(a, b, c) else "tilewise"
     if executor == "fused":
         if not _can_fuse(a, b, c):
-            raise RuntimeError("the fused executor needs a CUDA world and bfloat16 A / B")
+            raise RuntimeError("the fused executor needs a CUDA world and bfloat16 (or float32) A / B")
         if rep_c > 1 and not fuse_replica_reduce and T.my_replica(c.layout, c.rank) != 0:
             c.local_padded.zero_()
         _run_fused(kind, a, b, c, ops, fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta)
