@@ -121,6 +121,25 @@ def main() -> None:
         ms = timed(world, fused_wide, args.iters)
         st.check()
         out[f"fused_fetch_wide_rows_gbs_{variant}"] = round(wide_rows * wide_k * 2 / ms / 1e6, 1)
+    # redistribute (block -> column partition, and row -> column with a bf16 -> fp32 change) into an existing matrix:
+    # one-sided pulls of the overlapping pieces plus two device barriers per call
+    if size > 1:
+        side = 8192
+        src_m = ug.empty(world, (side, side), "block", torch.bfloat16)
+        src_m.local.normal_()
+        dst_m = ug.empty(world, (side, side), "column", torch.bfloat16)
+        sync_all(world)
+        ms = timed(world, lambda: ug.redistribute(src_m, "column", out=dst_m), args.iters)
+        moved = side * side * 2 / size                      # bytes every rank receives
+        out["redistribute_block_to_column_gbs_per_gpu"] = round(moved / ms / 1e6, 1)
+        out["redistribute_block_to_column_ms"] = round(ms, 4)
+        row_m = ug.empty(world, (side, side), "row", torch.bfloat16)
+        row_m.local.normal_()
+        dst32 = ug.empty(world, (side, side), "column", torch.float32)
+        sync_all(world)
+        ms = timed(world, lambda: ug.redistribute(row_m, "column", dtype=torch.float32, out=dst32), args.iters)
+        out["redistribute_row_to_column_bf16_to_fp32_ms"] = round(ms, 4)
+        st.check()
     if rank == 0:
         print(json.dumps(out), flush=True)
     world.close()

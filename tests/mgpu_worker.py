@@ -124,8 +124,9 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--cases", default="small")
+    ap.add_argument("--world", default="", help='"symm_mem": symmetric allocations from torch symmetric memory')
     args = ap.parse_args()
-    world = ug.init(device=args.device)
+    world = ug.init(device=args.device, world=args.world or None)
     dev = world.device
     in_dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
     rank, size = world.rank, world.size

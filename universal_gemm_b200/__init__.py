@@ -34,7 +34,7 @@ from .parallel.plan import (  # noqa: F401
     group_ops, select_method,
 )
 from .parallel.symm import (  # noqa: F401
-    CudaIpcWorld, DistComm, EmulatedCluster, FileComm, GuardViolation, ShmWorld, SingleWorld, SymmHeap, World,
+    CudaIpcWorld, DistComm, EmulatedCluster, FileComm, GuardViolation, ShmWorld, SingleWorld, SymmHeap, SymmMemWorld, World,
 )
 from .parallel.matrix import DistMatrix, distribute_tensor, empty, resolve, zeros  # noqa: F401
 from .parallel.runtime import (  # noqa: F401
@@ -50,12 +50,13 @@ from .parallel import handler as mm_handler  # noqa: F401
 from .utils import profile, trace  # noqa: F401
 
 
-def init(backend: str | None = None, device=None, timeout_s: float = 10.0) -> World:
+def init(backend: str | None = None, device=None, timeout_s: float = 10.0, world: str | None = None) -> World:
     """Create the world for this process and make it the default.
 
     Under ``torchrun`` (``RANK`` / ``WORLD_SIZE`` set) this initialises ``torch.distributed``
     (``nccl`` when CUDA is available, else ``gloo``) and returns a :class:`CudaIpcWorld` or
-    :class:`ShmWorld`; without a launcher it returns a single-rank world.
+    :class:`ShmWorld`; without a launcher it returns a single-rank world.  ``world="symm_mem"`` (or
+    ``UGEMM_WORLD=symm_mem``) takes the symmetric allocations from torch's symmetric memory instead of CUDA IPC.
     """
     import os
 
@@ -72,11 +73,15 @@ def init(backend: str | None = None, device=None, timeout_s: float = 10.0) -> Wo
                 dist.init_process_group(backend or "nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
             else:
                 dist.init_process_group(backend or "gloo")
-        world: World = CudaIpcWorld(timeout_s=timeout_s) if use_cuda else ShmWorld()
+        kind = world or os.environ.get("UGEMM_WORLD", "")
+        if use_cuda and kind == "symm_mem":
+            made: World = SymmMemWorld(timeout_s=timeout_s)
+        else:
+            made = CudaIpcWorld(timeout_s=timeout_s) if use_cuda else ShmWorld()
     else:
-        world = SingleWorld(torch.device("cuda", torch.cuda.current_device()) if use_cuda else "cpu")
-    set_default_world(world)
-    return world
+        made = SingleWorld(torch.device("cuda", torch.cuda.current_device()) if use_cuda else "cpu")
+    set_default_world(made)
+    return made
 
 
 def check_status(device=None) -> None:

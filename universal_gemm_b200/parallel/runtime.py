@@ -367,18 +367,23 @@ class SignalPad:
 
 
 # ----------------------------------------------------------------------------- redistribute
-def redistribute(dt: Any, partition, replication_factor: int = 1, dtype: torch.dtype | None = None) -> DistMatrix:
+def redistribute(dt: Any, partition, replication_factor: int = 1, dtype: torch.dtype | None = None,
+                 out: DistMatrix | None = None) -> DistMatrix:
     """Return a copy of the matrix in another partition (collective).
 
     One-sided: every rank pulls the pieces of the source tiles that overlap its new tile straight from their
     owners (``ug_pull_2d`` over peer pointers on the GPU), then converts the dtype locally if asked
     (``ug_convert_2d``).  This is the data movement the plain DTensor path performs with NCCL collectives
-    (``redistribute`` in the reference's benchmark/matmul_bench_worker.py:96-105)."""
+    (``redistribute`` in the reference's benchmark/matmul_bench_worker.py:96-105).  ``out``: an existing matrix in
+    the target partition to fill instead of allocating one (allocation is a collective host operation)."""
     from .matrix import empty
 
     src = resolve(dt)
     world = src.world
-    out = empty(world, src.shape, partition, src.dtype if dtype is None else dtype, replication_factor)
+    if out is None:
+        out = empty(world, src.shape, partition, src.dtype if dtype is None else dtype, replication_factor)
+    elif out.shape != src.shape or out.world is not world:
+        raise ValueError("`out` must be a matrix of the same shape in the same world")
     staging = out if out.dtype == src.dtype else None
     mine = T.tile_bounds(out.layout, out.coord)
     tmp = None

@@ -315,6 +315,51 @@ class CudaIpcWorld(World):
         self.barrier()
 
 
+class SymmMemWorld(CudaIpcWorld):
+    """One process per GPU; symmetric allocations from ``torch.distributed._symmetric_memory`` (``empty`` +
+    ``rendezvous``, CUDA or NVSHMEM backend) instead of raw CUDA IPC.  The kernels see the same thing either way: a
+    table of peer pointers.  The role of the reference's ``symm_mem_example.py:23-30`` bring-up.
+
+    torch binds such allocations to an NVLink multicast object where the hardware offers one
+    (``multicast_ptr`` below is then non-zero); a rank that dies while bound can disturb its peers, so the
+    CUDA-IPC world stays the default and this one is opt-in (``ug.init(world="symm_mem")``)."""
+
+    def __init__(self, group=None, device: torch.device | None = None, timeout_s: float = 10.0, backend: str | None = None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self._symm_mem = symm_mem
+        if backend is not None:
+            symm_mem.set_backend(backend)
+        self._handles: list = []
+        super().__init__(group=group, device=device, timeout_s=timeout_s)
+
+    def _alloc_raw(self, nbytes: int, guard: int) -> SymmBuffer:
+        import torch.distributed as dist
+
+        nbytes = _round_up(max(int(nbytes), 1), _ALIGN)
+        with torch.cuda.device(self.device):
+            local = self._symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            group = self.group if self.group is not None else dist.group.WORLD
+            handle = self._symm_mem.rendezvous(local, group)
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+        if len(ptrs) != self.size or ptrs[self.rank] != local.data_ptr():
+            raise RuntimeError("symmetric-memory rendezvous returned an unexpected pointer table")
+        tensors: list[torch.Tensor | None] = [None] * self.size
+        tensors[self.rank] = local
+        self._handles.append(handle)
+
+        def closer(handle=handle):
+            torch.cuda.synchronize(self.device)
+            self.comm.barrier()                 # nobody still reads a peer's memory when the owners let go
+            if handle in self._handles:
+                self._handles.remove(handle)
+
+        buf = SymmBuffer(self, nbytes, ptrs, tensors, closer, guard)
+        buf.multicast_ptr = int(getattr(handle, "multicast_ptr", 0) or 0)
+        self._buffers.append(buf)
+        return buf
+
+
 # ----------------------------------------------------------------------------- CPU shared memory
 class ShmWorld(World):
     """CPU ranks of one node; allocations are shared files under /dev/shm."""
