@@ -87,6 +87,9 @@ def main() -> None:
     ap.add_argument("--peak-tflops", type=float, default=0.0, help="bf16 GEMM peak of one GPU (roofline fields)")
     ap.add_argument("--link-gbs", type=float, default=0.0, help="NVLink GB/s per direction per GPU (roofline fields)")
     ap.add_argument("--only-groups", default="", help="comma-separated experiment groups to keep (e.g. odd_cube,skinny)")
+    ap.add_argument("--dtensor-skip-mixed-block", action="store_true",
+                    help="skip dtensor cases that mix block with row / column partitions (torch refuses most of them: "
+                         "operands on different device meshes; each also costs new NCCL sub-groups)")
     ap.add_argument("--cuda-graph", action="store_true", help="replay each stationary GEMM from a captured CUDA graph")
     ap.add_argument("--max-cases", type=int, default=0)
     ap.add_argument("--only-methods", default="", help="comma-separated filter applied to the case list")
@@ -113,6 +116,11 @@ def main() -> None:
     if args.only_groups:
         keep_groups = set(parse_csv_list(args.only_groups))
         cases = [(s, mc) for s, mc in cases if s.experiment_group in keep_groups]
+    if args.dtensor_skip_mixed_block:
+        def mixed(mc):
+            parts = {mc.a_partition, mc.b_partition, mc.c_partition}
+            return "block" in parts and len(parts) > 1
+        cases = [(s, mc) for s, mc in cases if not (mc.method == "dtensor" and mixed(mc))]
     if args.max_m > 0:
         cases = [(s, mc) for s, mc in cases if s.m <= args.max_m]
     if args.max_cases > 0:

@@ -567,3 +567,20 @@ def test_fused_fp32_operands_emulated(method):
         assert cluster.check_guards() == 12
         want = full_c.double() + full_a.double() @ full_b.double()
         torch.testing.assert_close(mats[0][2].full_tensor().double(), want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("m,n,k,tile_m", [(3001, 3001, 3001, "pair"), (3001, 3001, 3001, 256), (12289, 1537, 3001, 128),
+                                          (64, 16383, 16383, None), (1537, 12289, 12289, "pair512")])
+def test_gemm_kernel_large_odd_shapes(m, n, k, tile_m):
+    """Odd sizes of the benchmark sweep at kernel level: odd pitches put A and B on the 2-byte gather path of the
+    fetch warps, C is written with ragged right and bottom edges, M = 64 leaves most tensor rows empty."""
+    from universal_gemm_b200.ops import native
+    from universal_gemm_b200.ops.gemm import gemm
+
+    torch.manual_seed(m + n)
+    a = torch.randn(m, k, device=_dev()).bfloat16()
+    b = (torch.randn(k, n, device=_dev()) / k ** 0.5).bfloat16()
+    c = torch.full((m, n), 2.0, device=_dev())
+    gemm(a, b, c, mode=native.C_ADD, tile_m=tile_m)
+    _status_ok()
+    torch.testing.assert_close(c, a.float() @ b.float() + 2.0, rtol=3e-3, atol=3e-3)

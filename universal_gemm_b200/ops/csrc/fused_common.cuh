@@ -527,6 +527,11 @@ __device__ __forceinline__ float4 ld_stream_f4(const void* p) {
   const uint4 u = ld_stream_v4(p);
   return make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
 }
+__device__ __forceinline__ uint16_t ld_stream_u16(const void* p) {
+  uint16_t v;
+  asm volatile("ld.global.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ float ld_stream_f1(const void* p) {
   float v;
   asm volatile("ld.global.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
@@ -636,20 +641,36 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
       }
     }
   } else {
-    for (int64_t i = lane; i < total; i += 32) {
-      int r = static_cast<int>(i / vec_per_row);
-      int c = static_cast<int>(i - static_cast<int64_t>(r) * vec_per_row);
-      const uint16_t* s = reinterpret_cast<const uint16_t*>(src + r * pc.src_ld + (static_cast<int64_t>(c) << 4));
-      int valid = min(8, (pc.row_bytes - (c << 4)) >> 1);
-      uint16_t e[8];
+    // Source only 2-byte aligned (odd column offsets or pitches of odd-shaped partitions): every 16-byte destination
+    // vector is gathered from eight 2-byte loads; four vectors per lane and batch keep 32 loads in flight.
+    constexpr uint32_t U = 4;
+    const uint32_t vpr = static_cast<uint32_t>(vec_per_row);
+    const uint32_t nvec = static_cast<uint32_t>(total);
+    for (uint32_t base = 0; base < nvec; base += 32u * U) {
+      uint16_t e[U][8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) e[k] = (k < valid) ? s[k] : static_cast<uint16_t>(0);
-      uint4 out;
-      out.x = e[0] | (static_cast<uint32_t>(e[1]) << 16);
-      out.y = e[2] | (static_cast<uint32_t>(e[3]) << 16);
-      out.z = e[4] | (static_cast<uint32_t>(e[5]) << 16);
-      out.w = e[6] | (static_cast<uint32_t>(e[7]) << 16);
-      *reinterpret_cast<uint4*>(dst + r * pc.dst_ld + (static_cast<int64_t>(c) << 4)) = out;
+      for (uint32_t u = 0; u < U; ++u) {
+        const uint32_t idx = min(base + u * 32u + static_cast<uint32_t>(lane), nvec - 1u);
+        const uint32_t r = idx / vpr, c = idx - r * vpr;
+        const uint16_t* sp = reinterpret_cast<const uint16_t*>(src + static_cast<int64_t>(r) * pc.src_ld + (static_cast<int64_t>(c) << 4));
+        const int valid = min(8, (pc.row_bytes - static_cast<int>(c << 4)) >> 1);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) e[u][k] = (k < valid) ? ld_stream_u16(sp + k) : static_cast<uint16_t>(0);
+      }
+      asm volatile("" ::: "memory");
+#pragma unroll
+      for (uint32_t u = 0; u < U; ++u) {
+        const uint32_t idx = base + u * 32u + static_cast<uint32_t>(lane);
+        if (idx < nvec) {
+          const uint32_t r = idx / vpr, c = idx - r * vpr;
+          uint4 out;
+          out.x = e[u][0] | (static_cast<uint32_t>(e[u][1]) << 16);
+          out.y = e[u][2] | (static_cast<uint32_t>(e[u][3]) << 16);
+          out.z = e[u][4] | (static_cast<uint32_t>(e[u][5]) << 16);
+          out.w = e[u][6] | (static_cast<uint32_t>(e[u][7]) << 16);
+          *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * pc.dst_ld + (static_cast<int64_t>(c) << 4)) = out;
+        }
+      }
     }
   }
 }
