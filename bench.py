@@ -62,6 +62,8 @@ def parse_args(argv=None):
     ap.add_argument("--replication", type=int, default=1)
     ap.add_argument("--method", default="auto", choices=["auto", "stationary_c", "stationary_b"])
     ap.add_argument("--c-dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--operand-dtype", default="bf16", choices=["bf16", "fp32"],
+                    help="fp32: A and B are fp32 like the reference worker's; the kernel runs them as three bf16 products")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-verify", action="store_true")
     ap.add_argument("--no-context", action="store_true", help="skip the stock-DTensor bf16 comparator")
@@ -105,7 +107,8 @@ def _verify(ug, world, a, b, c, c_dtype, rows_per_rank: int = 64):
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     try:
-        want = full_a[rows].float() @ full_b.float()
+        want = (full_a[rows].double() @ full_b.double()).float() if full_a.dtype == torch.float32 \
+            else full_a[rows].float() @ full_b.float()
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
     got = full_c[rows].float()
@@ -136,15 +139,16 @@ def run_ours(args) -> dict:
     warmup = max(args.warmup, 3)
     rounds = max(args.rounds, 5)
 
-    a = ug.empty(world, (m, k), args.a_partition, torch.bfloat16, args.replication)
-    b = ug.empty(world, (k, n), args.b_partition, torch.bfloat16, args.replication)
+    in_dtype = torch.bfloat16 if args.operand_dtype == "bf16" else torch.float32
+    a = ug.empty(world, (m, k), args.a_partition, in_dtype, args.replication)
+    b = ug.empty(world, (k, n), args.b_partition, in_dtype, args.replication)
     c = ug.zeros(world, (m, n), args.c_partition, c_dtype, args.replication)
     # Every rank draws the same full matrices from one seed and keeps its shards (replicas hold equal copies).
     g = torch.Generator(device=dev).manual_seed(20260218)
     a.local_padded.zero_()
     b.local_padded.zero_()
-    a.fill_from_full((torch.randn(m, k, generator=g, device=dev) * 0.02).bfloat16())
-    b.fill_from_full((torch.randn(k, n, generator=g, device=dev) * 0.02).bfloat16())
+    a.fill_from_full((torch.randn(m, k, generator=g, device=dev) * 0.02).to(in_dtype))
+    b.fill_from_full((torch.randn(k, n, generator=g, device=dev) * 0.02).to(in_dtype))
     method = ug.select_method(args.method, b.layout, c.layout)
 
     def step():
@@ -181,10 +185,10 @@ def run_ours(args) -> dict:
     # of step i-1 while step i runs; all K copies and K read-backs happen inside the timed region.
     e2e, checks = None, []
     if not args.no_e2e:
-        a_alt = ug.empty(world, (m, k), args.a_partition, torch.bfloat16, args.replication)
+        a_alt = ug.empty(world, (m, k), args.a_partition, in_dtype, args.replication)
         a_alt.local_padded.zero_()
         bufs = (a, a_alt)
-        host_a = torch.empty(a.local.shape, dtype=torch.bfloat16).pin_memory()
+        host_a = torch.empty(a.local.shape, dtype=in_dtype).pin_memory()
         host_a.copy_(a.local)
         host_out = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
         copy_stream = torch.cuda.Stream(device=dev)
@@ -308,14 +312,19 @@ def run_ours(args) -> dict:
         ug.check_status(dev)
 
     context = None
-    if not args.no_context:
+    if not args.no_context and in_dtype == torch.bfloat16:
         # Stock DTensor (sharding propagation + NCCL redistribute + cuBLAS) on the same bf16 shards, same launch,
         # same timing.  This is a library baseline measured by this script, not the reference arm.
         try:
             import torch.distributed as dist
 
-            if not dist.is_initialized():
-                dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{args.master_port}", rank=0, world_size=1)
+            if not dist.is_initialized():       # one GPU without a launcher: DTensor still wants a process group
+                import socket
+
+                with socket.socket() as sock:
+                    sock.bind(("127.0.0.1", 0))
+                    port = sock.getsockname()[1]
+                dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
             from benchmark.matmul_bench_worker import _dtensor_iteration
 
             dt_a, dt_b = a.to_dtensor(), b.to_dtensor()
@@ -343,7 +352,9 @@ def run_ours(args) -> dict:
         "metric": METRIC,
         "value": value, "unit": "TFLOP/s", "n_gpus": world.size, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init N(0, 0.02) weights and activations)",
+        "vs_baseline": None,
+        "dtype": "bf16" if in_dtype == torch.bfloat16 else "fp32 operands as three bf16 products (hi x hi + hi x lo + lo x hi)",
+        "data": "synthetic (random-init N(0, 0.02) weights and activations)",
         "impl": "ours", "gpu_launches": launches, "rounds": rounds, "rounds_ms": [round(x, 4) for x in rounds_ms],
         "clocks": clocks, "e2e": e2e, "verified": verified, "breakdown": breakdown, "context": context,
         "config": {"model": "GPT-3-175B MLP up-projection GEMM" if (n, k) == (49152, 12288) else "GEMM",

@@ -54,7 +54,7 @@ def summarize(rows: list[dict]) -> str:
         big = [k for k in cases if k[0] in ("square", "gpt3_expansion", "gpt3_shrinking")]
         if big:
             out.append("| M x N x K | A,B,C | rep | dtensor bf16 | St-C fp32 C | St-B fp32 C | St-C bf16 C | St-B bf16 C | "
-                       "best fp32 C / dtensor | best / dtensor | roofline fraction (best fp32 C) | max abs err |")
+                       "best fp32 C / dtensor | best / dtensor | roofline fraction (best fp32 C) | max abs err (fp32 C) |")
             out.append("|---|---|---|---|---|---|---|---|---|---|---|---|")
             for key in big:
                 slot = cases[key]
@@ -64,7 +64,7 @@ def summarize(rows: list[dict]) -> str:
                 dt = g("dtensor")
                 b32 = max(ours32, key=lambda r: r["median_tflops"]) if ours32 else None
                 ball = max(ours, key=lambda r: r["median_tflops"]) if ours else None
-                errs = [r.get("max_abs_error") for r in ours if r.get("max_abs_error") is not None]
+                errs = [r.get("max_abs_error") for r in ours32 if r.get("max_abs_error") is not None]
                 out.append("| {} x {} x {} | {},{},{} | {} | {} | {} | {} | {} | {} | {} | {} | {} | {} |".format(
                     key[1], key[2], key[3], key[4], key[5], key[6], key[7], fmt(dt), fmt(g("stationary_c/fp32")),
                     fmt(g("stationary_b/fp32")), fmt(g("stationary_c/bf16")), fmt(g("stationary_b/bf16")),
