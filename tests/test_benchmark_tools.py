@@ -118,3 +118,29 @@ def test_plumbing_config_cpu_gloo_1024(tmp_path, method):
     rec = json.loads(result.read_text())
     assert rec["method"] == method and rec["world_size"] == 2 and (rec["m"], rec["n"], rec["k"]) == (1024, 1024, 1024)
     assert rec["max_abs_error"] is not None and rec["max_abs_error"] < 1e-2 and rec["median_tflops"] > 0
+
+
+def test_sweep_summary_tables(tmp_path):
+    """summarize_sweep.py: ratio against the dtensor comparator, best-of columns, odd-shape win count."""
+    import summarize_sweep as S
+
+    def row(method, tflops, group="gpt3_expansion", m=8192, n=49152, k=12288, c_dtype="fp32", triple=("row", "column", "row"), **kw):
+        base = {"experiment_group": group, "m": m, "n": n, "k": k, "a_partition": triple[0], "b_partition": triple[1],
+                "c_partition": triple[2], "replication_factor": 1, "world_size": 8, "method": method,
+                "median_tflops": tflops, "c_dtype": c_dtype, "max_abs_error": 1e-5, "roofline_fraction": 0.8,
+                "executed_method": "stationary_b", "tile_variant": "pair"}
+        base.update(kw)
+        return base
+
+    rows = [row("dtensor", 4000.0), row("stationary_c", 5000.0), row("stationary_b", 9000.0),
+            row("stationary_b", 9500.0, c_dtype="bf16"),
+            row("dtensor", 100.0, group="skinny", m=64, n=16383, k=16383), row("auto", 250.0, group="skinny", m=64, n=16383, k=16383)]
+    path = tmp_path / "results.json"
+    path.write_text(json.dumps({"results": rows}))
+    text = S.summarize(S.load([str(path)]))
+    assert "### 8 GPUs" in text
+    big = [ln for ln in text.splitlines() if ln.startswith("| 8192 x 49152 x 12288")][0]
+    cells = [c.strip() for c in big.strip("|").split("|")]
+    assert cells[3:8] == ["4000", "5000", "9000", "-", "9500"] and cells[8] == "2.25" and cells[9] == "2.38"
+    assert "auto >= dtensor bf16 on 1 of 1 odd / skinny cases." in text
+    assert S.main([str(path), "--output", str(tmp_path / "t.md")]) == 0 and (tmp_path / "t.md").read_text().startswith("### 8 GPUs")

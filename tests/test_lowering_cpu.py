@@ -114,3 +114,57 @@ def test_model_time_matches_the_measured_scale():
         b.add_task(_task(8192, 8192, 8192))
         assert abs(b.model_us(variant) - measured_us) / measured_us < 0.10, (variant, b.model_us(variant))
     assert FusedProgramBuilder("cpu", num_sms=1).model_us("pair") is None
+
+
+def test_split_k_cuts_atomic_tasks_into_whole_k_blocks():
+    """8 tiles on 148 workers with 256 K blocks each: every task becomes parts of whole K blocks that cover K once."""
+    t = _task(64, 2048, 16383, mode=native.C_ATOMIC)
+    out = FusedProgramBuilder._split_k([t], 128, 148)
+    assert len(out) == 18                                    # 148 // 8 tiles = 18 parts
+    spans = [(a.col0, a.cols, b.row0, b.rows) for part in out for a, b in part.segments]
+    assert all(a0 == b0 and ac == br for a0, ac, b0, br in spans)
+    assert sorted(a0 for a0, *_ in spans) == [a0 for a0, *_ in spans] and spans[0][0] == 0
+    assert sum(ac for _, ac, _, _ in spans) == 16383 and all(ac % 64 == 0 for _, ac, _, _ in spans[:-1])
+    assert all(p.c_ptr == t.c_ptr and p.m == 64 and p.n == 2048 and p.c_mode == native.C_ATOMIC for p in out)
+    # stores cannot be split (parts would overwrite each other), nor can plans that fill the GPU already
+    assert FusedProgramBuilder._split_k([_task(64, 2048, 16383, mode=native.C_STORE)], 128, 148)[0].segments == \
+        _task(64, 2048, 16383, mode=native.C_STORE).segments
+    many = [_task(1024, 6144, 12288, mode=native.C_ATOMIC) for _ in range(8)]
+    assert FusedProgramBuilder._split_k(many, 256, 74) == many
+
+
+def test_row_tasks_that_share_b_are_merged_into_a_stacked_task():
+    """Eight tasks of 8 rows each (A row tiles of a skinny problem on 8 ranks) with the same B slice become one task of
+    64 rows whose A is the stack of the eight slices and whose output rows go to eight places."""
+    from universal_gemm_b200.ops.fused import StackedSlice
+
+    k, n = 2048, 512
+    bslice = OperandSlice(base=1 << 20, ld=n, row0=0, col0=0, rows=k, cols=n)
+    b = FusedProgramBuilder("cpu", num_sms=148, split_k=True)
+    for i in range(8):
+        a = OperandSlice(base=(2 + i) << 20, ld=k, row0=0, col0=0, rows=8, cols=k, remote=i != 3)
+        b.add_task(TaskSpec(c_ptr=(64 + i) << 20, ldc=n, m=8, n=n, c_mode=native.C_ATOMIC, c_dtype=native.DT_F32,
+                            segments=[(a, bslice)], c_remote=i != 3))
+    other = _task(300, 200, 157, mode=native.C_ATOMIC)           # 300 rows: left alone
+    b.add_task(other)
+    assert b.merge_row_tasks() == 7
+    merged, untouched = b.tasks
+    assert untouched is other
+    a_stack, b_same = merged.segments[0]
+    assert isinstance(a_stack, StackedSlice) and a_stack.rows == 64 and a_stack.cols == k and b_same == bslice
+    assert merged.m == 64 and merged.c_rows == tuple(((64 + i) << 20, n, 8) for i in range(8)) and merged.c_remote
+    assert [off for _, off in a_stack.row_parts()] == list(range(0, 64, 8)) and not a_stack.tma_ok()
+    assert a_stack.with_cols(128, 64).parts[5].col0 == 128 and a_stack.remote_bytes() == 7 * 8 * k * 2
+    # tasks whose B slices differ are not merged
+    b2 = FusedProgramBuilder("cpu", num_sms=148)
+    for i in range(2):
+        b2.add_task(TaskSpec(c_ptr=(64 + i) << 20, ldc=n, m=8, n=n, c_mode=native.C_ATOMIC, c_dtype=native.DT_F32,
+                             segments=[(OperandSlice((2 + i) << 20, k, 0, 0, 8, k),
+                                        OperandSlice(1 << 20, 2 * n, 0, i * n, k, n))]))
+    assert b2.merge_row_tasks() == 0 and len(b2.tasks) == 2
+
+
+def test_split_fp32_slices_are_always_staged():
+    hi = OperandSlice(base=4096, ld=128, row0=0, col0=0, rows=16, cols=64, elem_bytes=4, split=1)
+    assert not hi.tma_ok() and hi.vector_ok() and hi.with_split(2).split == 2
+    assert hi.address(1, 2) == 4096 + (128 + 2) * 4
