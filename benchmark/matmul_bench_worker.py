@@ -27,7 +27,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import universal_gemm_b200 as ug  # noqa: E402
 from universal_gemm_b200.utils.benchmarking import max_over_ranks, sync_all  # noqa: E402
 
-METHODS = ("dtensor", "stationary_c", "stationary_b", "auto")
+METHODS = ("dtensor", "stationary_c", "stationary_b", "auto", "min_traffic")
 DTYPES = {"bf16": torch.bfloat16, "fp32": torch.float32}
 
 
@@ -110,7 +110,8 @@ def bench_case(world, args: argparse.Namespace) -> BenchResult | None:
             a = ug.distribute_tensor(full_a, world, args.a_partition, args.replication_factor)
             b = ug.distribute_tensor(full_b, world, args.b_partition, args.replication_factor)
             c = ug.zeros(world, (m, n), args.c_partition, c_dtype, args.replication_factor)
-            executed = ug.select_method(args.method, b.layout, c.layout)
+            executed = ug.select_method(args.method, b.layout, c.layout, a.layout, in_bytes=a.itemsize,
+                                        c_bytes=c.itemsize)
             mats = (a, b, c)
 
             if world.is_cuda and getattr(args, "cuda_graph", False) and in_dtype == torch.bfloat16:

@@ -160,3 +160,24 @@ def test_auto_rule_and_cache():
     assert ug.build_stationary_c_ops(a, b, c, rank=1) is not first
     with pytest.raises(ValueError):
         ug.build_stationary_c_ops(a, b, c2, rank=0)
+
+
+def test_min_traffic_method_selection():
+    """GPT-3 up-projection with B split along K (row / row / row) on 8 ranks: Stationary-B ships 7/8 of an fp32 partial C
+    per rank (1.4 GB), Stationary-C pulls 7/8 of B (1.06 GB), so ``min_traffic`` takes Stationary-C where the reference's
+    size rule (K > M) takes Stationary-B; with a bf16 C the push halves and Stationary-B wins.  With a column-split B
+    (row / column / row) both rules agree on Stationary-B."""
+    from universal_gemm_b200.parallel import partition as PT, plan as PL
+
+    m, n, k = 8192, 49152, 12288
+    lay = lambda shape, part: PT.get_partitioning(part, 1, 8).layout(shape)  # noqa: E731
+    a, b, c = lay((m, k), "row"), lay((k, n), "row"), lay((m, n), "row")
+    assert PL.select_method("auto", b, c) == "stationary_b"
+    tb, tc = PL.plan_traffic("stationary_b", a, b, c), PL.plan_traffic("stationary_c", a, b, c)
+    assert tb == (7 * 1024 * 1536 * 2, 7 * 1024 * n * 4) and tc == (7 * 1536 * n * 2, 0)
+    assert PL.select_method("min_traffic", b, c, a) == "stationary_c"
+    assert PL.select_method("min_traffic", b, c, a, c_bytes=2) == "stationary_b"
+    b_col = lay((k, n), "column")
+    assert PL.select_method("min_traffic", b_col, c, a) == PL.select_method("auto", b_col, c) == "stationary_b"
+    with pytest.raises(ValueError):
+        PL.select_method("min_traffic", b, c)

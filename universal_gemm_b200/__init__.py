@@ -31,7 +31,7 @@ from .parallel.partition import (  # noqa: F401
 from .parallel.plan import (  # noqa: F401
     MultiplyOp, build_stationary_b_ops, build_stationary_c_ops, clear_plan_cache, clear_stationary_b_plan_cache,
     clear_stationary_c_plan_cache, format_op, format_plan, format_stationary_b_op, format_stationary_b_plan,
-    group_ops, select_method,
+    group_ops, plan_traffic, select_method,
 )
 from .parallel.symm import (  # noqa: F401
     CudaIpcWorld, DistComm, EmulatedCluster, FileComm, GuardViolation, ShmWorld, SingleWorld, SymmHeap, SymmMemWorld, World,

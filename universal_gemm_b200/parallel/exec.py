@@ -337,8 +337,9 @@ def row_partitioned_matmul(a: Any, b: Any, c: Any, **kwargs) -> list[MultiplyOp]
 
 
 def matmul(a: Any, b: Any, c: Any, *, method: str = "auto", **kwargs) -> list[MultiplyOp]:
-    """``C += A @ B`` with ``method`` in {auto, stationary_c, stationary_b}."""
-    chosen = P.select_method(method, resolve(b).layout, resolve(c).layout)
+    """``C += A @ B`` with ``method`` in {auto, stationary_c, stationary_b, min_traffic}."""
+    ra, rb, rc = resolve(a), resolve(b), resolve(c)
+    chosen = P.select_method(method, rb.layout, rc.layout, ra.layout, in_bytes=ra.itemsize, c_bytes=rc.itemsize)
     if chosen == "stationary_b":
         return execute_stationary_b(a, b, c, **kwargs)
     return execute_stationary_c(a, b, c, **kwargs)

@@ -46,7 +46,7 @@ from .tiles import (
     _current_rank,
 )
 
-STATIONARY_METHODS = ("auto", "stationary_c", "stationary_b")
+STATIONARY_METHODS = ("auto", "stationary_c", "stationary_b", "min_traffic")
 
 
 @dataclass(frozen=True)
@@ -234,14 +234,52 @@ def validate_op_shapes(op: MultiplyOp) -> None:
         raise RuntimeError(f"Bad op (N mismatch): {op}")
 
 
-def select_method(method: str, b: Any, c: Any) -> str:
+def select_method(method: str, b: Any, c: Any, a: Any = None, *, in_bytes: int = 2, c_bytes: int = 4) -> str:
     """``auto`` picks Stationary-B when B has more elements than C (K > M), else Stationary-C
-    (rule of the reference's dtensor_mm_handler.py:109-114)."""
+    (rule of the reference's dtensor_mm_handler.py:109-114).  ``min_traffic`` (not in the reference; needs ``a``)
+    picks the method whose busiest rank moves fewer bytes over the links, see :func:`plan_traffic`; the reference's
+    rule decides ties."""
     if method not in STATIONARY_METHODS:
-        raise ValueError("stationary_method must be one of: auto, stationary_c, stationary_b")
-    if method != "auto":
+        raise ValueError("stationary_method must be one of: auto, stationary_c, stationary_b, min_traffic")
+    by_size = "stationary_b" if matrix_numel(b) > matrix_numel(c) else "stationary_c"
+    if method == "auto":
+        return by_size
+    if method != "min_traffic":
         return method
-    return "stationary_b" if matrix_numel(b) > matrix_numel(c) else "stationary_c"
+    if a is None:
+        raise ValueError("min_traffic needs the layout of A as well")
+    cost = {m: max(plan_traffic(m, a, b, c, in_bytes=in_bytes, c_bytes=c_bytes)) for m in ("stationary_b", "stationary_c")}
+    if cost["stationary_b"] == cost["stationary_c"]:
+        return by_size
+    return min(cost, key=cost.get)
+
+
+def plan_traffic(method: str, a: Any, b: Any, c: Any, *, in_bytes: int = 2, c_bytes: int = 4) -> tuple[int, int]:
+    """Bytes the busiest rank pulls in (operand slices of tiles it does not own) and pushes out (partial C for tiles
+    it does not own) in one execution of ``method``: the link-side cost of a plan.  With a replicated C every replica
+    pushes into replica 0 (the fused replica reduction)."""
+    kind = "b" if method == "stationary_b" else "c"
+    la, lb, lc = (as_layout(x) for x in (a, b, c))
+    push_to_origin = replication_factor(lc) > 1
+    worst_in = worst_out = 0
+    for rank in lc.ranks():
+        ops = _build(kind, la, lb, lc, True, rank)
+        seen_a: set = set()
+        seen_b: set = set()
+        bytes_in = bytes_out = 0
+        for op in ops:
+            if tile_rank(la, op.a_idx, rank=rank) != rank and (op.a_idx, op.a_slice) not in seen_a:
+                seen_a.add((op.a_idx, op.a_slice))
+                bytes_in += op.a_slice.shape[0] * op.a_slice.shape[1] * in_bytes
+            if tile_rank(lb, op.b_idx, rank=rank) != rank and (op.b_idx, op.b_slice) not in seen_b:
+                seen_b.add((op.b_idx, op.b_slice))
+                bytes_in += op.b_slice.shape[0] * op.b_slice.shape[1] * in_bytes
+        for region in group_ops(ops):
+            owner = tile_rank(lc, region.c_idx, replica=0 if push_to_origin else None, rank=rank)
+            if owner != rank:
+                bytes_out += region.c_slice.shape[0] * region.c_slice.shape[1] * c_bytes
+        worst_in, worst_out = max(worst_in, bytes_in), max(worst_out, bytes_out)
+    return worst_in, worst_out
 
 
 # ----------------------------------------------------------------------------- regions
