@@ -598,10 +598,42 @@ __device__ __forceinline__ void copy_piece_split_f32(const UgPiece& pc, int lane
   }
 }
 
+// Mode 0 (16-byte aligned source): the piece is walked as one flat sequence of 16-byte vectors (row after row); a
+// warp takes 32 x U consecutive vectors per batch, whatever the piece's shape (one 24 KiB row or 128 rows of 256
+// bytes).  The batch is straight-line code: U unconditional loads (lanes past the end re-read the last vector), a
+// compiler barrier, then the predicated stores, so one warp keeps U x 512 bytes on the wire: over NVLink the copy
+// rate is (bytes in flight) / (about 2 us of latency), and a copy loop whose loads are issued one at a time reaches
+// a quarter of the link rate.  U is chosen per launch (UgFusedParams::fetch_depth): loads in flight share the SM's
+// outstanding-request capacity with the TMA operand loads, so a plan that needs its remote data slowly asks for less.
+template <uint32_t U>
+__device__ __forceinline__ void copy_flat_vec(const UgPiece& pc, int lane, int vec_per_row, uint32_t nvec) {
+  const char* src = reinterpret_cast<const char*>(pc.src);
+  char* dst = reinterpret_cast<char*>(pc.dst);
+  const uint32_t vpr = static_cast<uint32_t>(vec_per_row);
+  for (uint32_t base = 0; base < nvec; base += 32u * U) {
+    uint4 buf[U];
+#pragma unroll
+    for (uint32_t u = 0; u < U; ++u) {
+      const uint32_t idx = min(base + u * 32u + static_cast<uint32_t>(lane), nvec - 1u);
+      const uint32_t r = idx / vpr, c = idx - r * vpr;
+      buf[u] = ld_stream_v4(src + static_cast<int64_t>(r) * pc.src_ld + (static_cast<int64_t>(c) << 4));
+    }
+    asm volatile("" ::: "memory");
+#pragma unroll
+    for (uint32_t u = 0; u < U; ++u) {
+      const uint32_t idx = base + u * 32u + static_cast<uint32_t>(lane);
+      if (idx < nvec) {
+        const uint32_t r = idx / vpr, c = idx - r * vpr;
+        *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * pc.dst_ld + (static_cast<int64_t>(c) << 4)) = buf[u];
+      }
+    }
+  }
+}
+
 // Copy one piece with the 32 lanes of a warp.  mode 0: 16-byte vectors, sixteen in
 // flight per lane.  mode 1: the source is only 2-byte aligned; every 16-byte
 // destination vector is gathered from eight 2-byte loads.
-__device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
+__device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane, int depth) {
   const int vec_per_row = (pc.row_bytes + 15) >> 4;
   if (vec_per_row <= 0) return;
   const int64_t total = static_cast<int64_t>(pc.rows) * vec_per_row;
@@ -613,33 +645,9 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane) {
     return;
   }
   if (mode == 0) {
-    // The piece is walked as one flat sequence of 16-byte vectors (row after row); a warp takes 32 x U consecutive
-    // vectors per batch, whatever the piece's shape (one 24 KiB row or 128 rows of 256 bytes).  The batch is
-    // straight-line code: U unconditional loads (lanes past the end re-read the last vector), a compiler barrier,
-    // then the predicated stores, so one warp keeps U x 512 bytes on the wire: over NVLink the copy rate is
-    // (bytes in flight) / (about 2 us of latency), and a copy loop whose loads are issued one at a time reaches
-    // a quarter of the link rate.
-    constexpr uint32_t U = 16;
-    const uint32_t vpr = static_cast<uint32_t>(vec_per_row);
-    const uint32_t nvec = static_cast<uint32_t>(total);
-    for (uint32_t base = 0; base < nvec; base += 32u * U) {
-      uint4 buf[U];
-#pragma unroll
-      for (uint32_t u = 0; u < U; ++u) {
-        const uint32_t idx = min(base + u * 32u + static_cast<uint32_t>(lane), nvec - 1u);
-        const uint32_t r = idx / vpr, c = idx - r * vpr;
-        buf[u] = ld_stream_v4(src + static_cast<int64_t>(r) * pc.src_ld + (static_cast<int64_t>(c) << 4));
-      }
-      asm volatile("" ::: "memory");
-#pragma unroll
-      for (uint32_t u = 0; u < U; ++u) {
-        const uint32_t idx = base + u * 32u + static_cast<uint32_t>(lane);
-        if (idx < nvec) {
-          const uint32_t r = idx / vpr, c = idx - r * vpr;
-          *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * pc.dst_ld + (static_cast<int64_t>(c) << 4)) = buf[u];
-        }
-      }
-    }
+    if (depth <= 4) copy_flat_vec<4>(pc, lane, vec_per_row, static_cast<uint32_t>(total));
+    else if (depth <= 8) copy_flat_vec<8>(pc, lane, vec_per_row, static_cast<uint32_t>(total));
+    else copy_flat_vec<16>(pc, lane, vec_per_row, static_cast<uint32_t>(total));
   } else {
     // Source only 2-byte aligned (odd column offsets or pitches of odd-shaped partitions): every 16-byte destination
     // vector is gathered from eight 2-byte loads; four vectors per lane and batch keep 32 loads in flight.

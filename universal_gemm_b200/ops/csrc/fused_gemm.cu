@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
         if (lane == 0) raise_error(ctl, UG_ERR_BAD_TABLE);
         break;
       }
-      copy_piece(pc, lane);
+      copy_piece(pc, lane, P.fetch_depth == 0 ? 16 : P.fetch_depth);
       __threadfence();
       __syncwarp();
       if (lane == 0) {

@@ -89,6 +89,8 @@ typedef struct {
   int32_t epi_poll_ns;       // pause between the epilogue warps' polls of the accumulator barrier (0 = none)
   uint64_t sched;            // 0 = static round-robin tiles; else uint32[2] {next tile claim, finished workers}, both
                              // zero at launch (the last worker to finish resets them): workers claim tiles dynamically
+  int32_t fetch_depth;       // 16-byte loads a fetch-warp lane keeps in flight: 4, 8 or 16 (0 means 16)
+  int32_t reserved0;
 } UgFusedParams;
 
 // Fields of one timeline record (globaltimer nanoseconds unless noted).  Record `trace_slots` of a CTA is

@@ -615,10 +615,18 @@ class FusedProgramBuilder:
         dynamic = pair if dyn_env == "" else dyn_env != "0"
         params.sched = base + int(offsets[6]) if dynamic else 0
         params.epi_poll_ns = int(os.environ.get("UGEMM_EPI_POLL_NS", "0"))
+        # Loads in flight per fetch-warp lane.  Sixteen reach the link rate (450-530 GB/s) but slow the main loops that
+        # run beside them by 25-40 % (the tiles' TMA loads and the fetch warps' loads share the SM's outstanding-request
+        # capacity, and loads over NVLink hold it three times as long); eight still copy at 435 GB/s and cost 10 %.
+        # A plan that needs its remote bytes no faster than 300 GB/s over its modelled kernel time takes eight.
+        remote_total = sum(st.src.remote_bytes() for st in staged.values() if st.pieces_of is None)
+        modelled_us = self.model_us(variant) or 0.0
+        need_gbs = remote_total / (modelled_us * 1e3) if modelled_us > 0 else float("inf")
+        params.fetch_depth = int(os.environ.get("UGEMM_FETCH_DEPTH", "0")) or (8 if need_gbs < 300.0 else 16)
         params.timeout_ns = self.timeout_ns
         stats = dict(tasks=len(task_rows), segments=len(seg_rows), tiles=total_tiles, maps=len(map_specs),
                      pieces=len(ordered), staged_bytes=staging_bytes, tile_m=variant if pair else BM,
-                     indirect_rows=len(row_table),
+                     indirect_rows=len(row_table), fetch_depth=int(params.fetch_depth),
                      push_bytes=sum(t.m * t.n * (4 if t.c_dtype == native.DT_F32 else 2) for t in tasks if t.c_remote),
                      model_us=round(self.model_us(variant) or 0.0, 1),
                      remote_bytes=sum(st.src.remote_bytes() for st in staged.values() if st.pieces_of is None),
