@@ -144,3 +144,20 @@ def test_sweep_summary_tables(tmp_path):
     assert cells[3:8] == ["4000", "5000", "9000", "-", "9500"] and cells[8] == "2.25" and cells[9] == "2.38"
     assert "auto >= dtensor bf16 on 1 of 1 odd / skinny cases." in text
     assert S.main([str(path), "--output", str(tmp_path / "t.md")]) == 0 and (tmp_path / "t.md").read_text().startswith("### 8 GPUs")
+
+
+def test_bench_reference_arm_without_gpu_reports_unavailable_and_arms_share_the_metric():
+    """``bench.py --impl reference`` on a machine without CUDA prints the one-line ``unavailable`` record and exits 0;
+    both arms take their ``metric`` string from ``bench.METRIC``; the reference arm imports nothing of the package."""
+    import torch
+
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "2"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    if not torch.cuda.is_available():
+        line = json.loads([ln for ln in proc.stdout.splitlines() if ln.startswith("{")][-1])
+        assert line["impl"] == "reference" and "unavailable" in line
+    src = open(os.path.join(ROOT, "baseline", "run_reference.py"), encoding="utf-8").read()
+    assert '"metric": metric' in src and "import universal_gemm_b200" not in src and "from universal_gemm_b200" not in src
+    bench_src = open(os.path.join(ROOT, "bench.py"), encoding="utf-8").read()
+    assert '"metric": METRIC' in bench_src and "run_reference.main(args, METRIC)" in bench_src
