@@ -330,18 +330,22 @@ def run_ours(args) -> dict:
             dt_a, dt_b = a.to_dtensor(), b.to_dtensor()
             for _ in range(3):
                 _dtensor_iteration(dt_a, dt_b)
-            sync_all(world)
-            d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = max(args.steps // 2, 5)
-            d0.record()
-            for _ in range(reps):
-                _dtensor_iteration(dt_a, dt_b)
-            d1.record()
-            sync_all(world)
-            dt_ms = max_over_ranks(d0.elapsed_time(d1) / reps, dev)
+            dt_rounds = []                     # same protocol as the timed region above: rounds of --steps steps
+            for _ in range(rounds):
+                d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                sync_all(world)
+                d0.record()
+                for _ in range(args.steps):
+                    _dtensor_iteration(dt_a, dt_b)
+                d1.record()
+                sync_all(world)
+                dt_rounds.append(max_over_ranks(d0.elapsed_time(d1) / args.steps, dev))
+            dt_ms = statistics.median(dt_rounds)
             context = {"dtensor_bf16_tflops": 2.0 * m * n * k / (dt_ms * 1e-3) / 1e12, "dtensor_bf16_ms_per_step": dt_ms,
+                       "rounds_ms": [round(x, 4) for x in dt_rounds],
                        "what": "torch DTensor matmul + redistribute of Partial results (NCCL + cuBLAS), bf16 operands, "
-                               "output placement chosen by DTensor; CUDA events, max over ranks"}
+                               "output placement chosen by DTensor; CUDA events, max over ranks, median of the same "
+                               "number of rounds and steps as `value`"}
         except Exception as exc:  # noqa: BLE001
             context = {"dtensor_bf16_tflops": None, "error": f"{type(exc).__name__}: {str(exc)[:160]}"}
 
