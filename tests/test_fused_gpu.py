@@ -584,3 +584,31 @@ def test_gemm_kernel_large_odd_shapes(m, n, k, tile_m):
     gemm(a, b, c, mode=native.C_ADD, tile_m=tile_m)
     _status_ok()
     torch.testing.assert_close(c, a.float() @ b.float() + 2.0, rtol=3e-3, atol=3e-3)
+
+
+@pytest.mark.parametrize("case", ["aligned", "odd", "skinny", "bf16_c", "replicated"])
+def test_epilogue_checksum_adds_up_to_the_sum_of_the_product(case):
+    """``checksum=``: every rank's kernel adds the sum of all values it writes into (or adds to) C to a running
+    double; over all ranks that is sum(A @ B), whatever path the epilogue takes (vector, shifted for odd columns,
+    row table of merged skinny tasks with K split, bf16 output, pushes into replica 0) and over repeated calls."""
+    m, n, k, triple, rep, c_dtype, world = {
+        "aligned": (1024, 1536, 512, ("row", "column", "row"), 1, torch.float32, 4),
+        "odd": (389, 517, 263, ("block", "column", "block"), 1, torch.float32, 4),
+        "skinny": (64, 2100, 4500, ("row", "column", "row"), 1, torch.float32, 8),
+        "bf16_c": (512, 777, 320, ("column", "row", "row"), 1, torch.bfloat16, 4),
+        "replicated": (512, 768, 640, ("row", "row", "row"), 2, torch.float32, 4),
+    }[case]
+    full_a, full_b, full_c = make_inputs(m, n, k, seed=51, device=_dev())
+    want = float((full_a.bfloat16().double() @ full_b.bfloat16().double()).sum().item())
+    scale = float((full_a.bfloat16().double() @ full_b.bfloat16().double()).abs().sum().item())
+    for method in ("stationary_c", "stationary_b"):
+        cluster = ug.EmulatedCluster(world, _dev())
+        mats = build_cluster_matrices(cluster, full_a, full_b, full_c, triple, rep, torch.bfloat16, c_dtype)
+        sums = [torch.zeros(1, dtype=torch.float64, device=_dev()) for _ in mats]
+        calls = 2
+        for _ in range(calls):
+            for (a, b, c), chk in zip(mats, sums):
+                ug.matmul(a, b, c, method=method, checksum=chk)
+        _status_ok()
+        got = sum(float(x.item()) for x in sums)
+        assert abs(got - calls * want) <= 1e-5 * scale + 1e-6, (case, method, got, calls * want)

@@ -401,6 +401,15 @@ __device__ __forceinline__ void store_chunk_scalar(float* sb, const uint32_t (&v
   __syncwarp();
 }
 
+// Sum of the accumulator columns [lo, hi) of this lane's row (the checksum a launch can ask for).
+__device__ __forceinline__ float sum_columns(const uint32_t (&v)[32], int lo, int hi) {
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (j >= lo && j < hi) s += __uint_as_float(v[j]);
+  return s;
+}
+
 // The same transpose for a 32-column chunk of which only columns [lo, hi) are to be written (lo a multiple of 4;
 // c_base 16-byte aligned): whole 16-byte groups inside the range go out as vectors, the ragged end element by element.
 __device__ __forceinline__ void store_chunk_f32_ragged(float* sb, const uint32_t (&v)[32], int lane, const CRows& rows,
@@ -450,7 +459,7 @@ __device__ __forceinline__ void store_chunk_f32_ragged(float* sb, const uint32_t
 // boundary of C.  `avail` TMEM columns can be read from `taddr`; a last chunk that would read past them is moved back
 // by a multiple of four columns and writes only what the chunks before it have not written.
 __device__ __forceinline__ void epilogue_drain_f32_shifted(uint32_t taddr, const UgTask& t, int row0, int col0,
-                                                           int n_rem, int avail, float* epi_buf, int lane) {
+                                                           int n_rem, int avail, float* epi_buf, int lane, float* acc) {
   const int rows_valid = min(32, t.m - row0);
   if (rows_valid <= 0) return;
   CRows rows;
@@ -471,6 +480,7 @@ __device__ __forceinline__ void epilogue_drain_f32_shifted(uint32_t taddr, const
   if (head > 0) {
     tmem_ld_32x32(taddr, v);
     tmem_ld_wait();
+    if (acc != nullptr && lane < rows_valid) *acc += sum_columns(v, 0, head);
     if (lane < rows_valid) {
       float* g = rows.row(lane);
 #pragma unroll
@@ -488,6 +498,7 @@ __device__ __forceinline__ void epilogue_drain_f32_shifted(uint32_t taddr, const
   for (; c < n_rem && c + 32 <= avail; c += 32) {
     tmem_ld_32x32(taddr + c, v);
     tmem_ld_wait();
+    if (acc != nullptr && lane < rows_valid) *acc += sum_columns(v, 0, min(32, n_rem - c));
     store_chunk_f32_ragged(epi_buf, v, lane, rows, c, rows_valid, t.c_mode, 0, min(32, n_rem - c));
   }
   if (c < n_rem) {
@@ -500,12 +511,14 @@ __device__ __forceinline__ void epilogue_drain_f32_shifted(uint32_t taddr, const
     if (lo < hi) {
       tmem_ld_32x32(taddr + start, v);
       tmem_ld_wait();
+      if (acc != nullptr && lane < rows_valid) *acc += sum_columns(v, lo, hi);
       store_chunk_f32_ragged(epi_buf, v, lane, rows, start, rows_valid, t.c_mode, lo, hi);
     }
     const int rem = n_rem - min(start + 32, n_rem);
     if (rem > 0) {
       tmem_ld_32x32(taddr + n_rem - 32, v);
       tmem_ld_wait();
+      if (acc != nullptr && lane < rows_valid) *acc += sum_columns(v, 32 - rem, 32);
       if (lane < rows_valid) {
         float* g = rows.row(lane) + n_rem - 32;
 #pragma unroll
@@ -688,11 +701,11 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane, int dept
 // columns col0.. of the task's C.  The common case (fp32 C, 16-byte aligned, whole 32-column chunks) is software
 // pipelined: the TMEM load of the next chunk is in flight while the current chunk goes through shared memory.
 __device__ __forceinline__ void epilogue_drain(uint32_t taddr, const UgTask& t, int row0, int col0, int n_rem,
-                                               int avail, float* epi_buf, int lane) {
+                                               int avail, float* epi_buf, int lane, float* acc) {
   const int rows_valid = min(32, t.m - row0);               // <= 0 when the warp is past the region
   if (t.c_dtype == 0 && task_c_pitch_vec(t) &&
       (task_c_rows_indirect(t) || !(task_c_vec(t) && (n_rem & 31) == 0 && (col0 & 3) == 0))) {
-    epilogue_drain_f32_shifted(taddr, t, row0, col0, n_rem, avail, epi_buf, lane);
+    epilogue_drain_f32_shifted(taddr, t, row0, col0, n_rem, avail, epi_buf, lane, acc);
     return;
   }
   if (task_c_vec(t) && t.c_dtype == 0 && (n_rem & 31) == 0) {
@@ -703,9 +716,11 @@ __device__ __forceinline__ void epilogue_drain(uint32_t taddr, const UgTask& t, 
       tmem_ld_wait();
       const bool second = c + 32 < n_rem;
       if (second) tmem_ld_32x32(taddr + c + 32, vb);
+      if (acc != nullptr && lane < rows_valid) *acc += sum_columns(va, 0, 32);
       store_chunk_f32(epi_buf, va, lane, c_row + c, t.ldc, rows_valid, t.c_mode);
       if (second) {
         tmem_ld_wait();
+        if (acc != nullptr && lane < rows_valid) *acc += sum_columns(vb, 0, 32);
         if (c + 64 < n_rem) tmem_ld_32x32(taddr + c + 64, va);
         store_chunk_f32(epi_buf, vb, lane, c_row + c + 32, t.ldc, rows_valid, t.c_mode);
       }
@@ -719,6 +734,7 @@ __device__ __forceinline__ void epilogue_drain(uint32_t taddr, const UgTask& t, 
       tmem_ld_32x32(taddr + c, v0);
       tmem_ld_32x32(taddr + c + 32, v1);
       tmem_ld_wait();
+      if (acc != nullptr && lane < rows_valid) *acc += sum_columns(v0, 0, 32) + sum_columns(v1, 0, 32);
       store_chunk_bf16_64(epi_buf, v0, v1, lane,
                           reinterpret_cast<__nv_bfloat16*>(t.c_ptr) + static_cast<int64_t>(row0) * t.ldc + col0 + c,
                           t.ldc, rows_valid, t.c_mode);
@@ -729,6 +745,7 @@ __device__ __forceinline__ void epilogue_drain(uint32_t taddr, const UgTask& t, 
     tmem_ld_32x32(taddr + c, v);
     tmem_ld_wait();
     const int ncols = min(32, n_rem - c);
+    if (acc != nullptr && lane < rows_valid) *acc += sum_columns(v, 0, ncols);
     const int64_t off0 = static_cast<int64_t>(row0) * t.ldc + col0 + c;
     if (task_c_vec(t) && ncols == 32) {
       if (t.c_dtype == 0)
@@ -740,6 +757,14 @@ __device__ __forceinline__ void epilogue_drain(uint32_t taddr, const UgTask& t, 
       store_chunk_scalar(epi_buf, v, lane, t.c_ptr, off0, t.ldc, rows_valid, ncols, t.c_mode, t.c_dtype);
     }
   }
+}
+
+// Add an epilogue warp's checksum share of one tile to the launch's checksum (a double in device memory).
+__device__ __forceinline__ void checksum_flush(uint64_t checksum_ptr, float acc, int lane) {
+  if (checksum_ptr == 0) return;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  if (lane == 0) atomicAdd(reinterpret_cast<double*>(checksum_ptr), static_cast<double>(acc));
 }
 
 }  // namespace ugfused

@@ -260,16 +260,19 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_kernel(const UgF
       // the two warps of a quadrant split the columns on a multiple of 64 (whole 128-byte row segments each)
       const int split = min(n_rem, ((n_rem + 127) >> 7) << 6);
       const int c0 = part == 0 ? 0 : split, cn = part == 0 ? split : n_rem - split;
+      float csum = 0.f;
+      float* acc_sum = P.checksum != 0 ? &csum : nullptr;
 #pragma unroll
       for (int h = 0; h < C::kHalves; ++h) {
         if (cn <= 0 || tc.mt * BM + h * 128 >= t.m) break;     // nothing to do (warp-uniform)
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                (C::kAccBufs == 2 ? acc * UG_BN : static_cast<uint32_t>(h) * UG_BN);
-        epilogue_drain(taddr + c0, t, tc.mt * BM + h * 128 + quad * 32, col0 + c0, cn, UG_BN - c0, epi_buf, lane);
+        epilogue_drain(taddr + c0, t, tc.mt * BM + h * 128 + quad * 32, col0 + c0, cn, UG_BN - c0, epi_buf, lane, acc_sum);
       }
       if (tracer) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->acc_empty[acc]));
+      checksum_flush(P.checksum, csum, lane);
       if (C::kAccBufs == 2) acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }

@@ -295,10 +295,14 @@ __global__ void __launch_bounds__(kNumThreads, 1) ug_fused_gemm_pair_kernel(cons
       // the two warps of a quadrant split the columns on a multiple of 64 (whole 128-byte row segments each)
       const int split = min(n_rem, ((n_rem + 127) >> 7) << 6);
       const int c0 = part == 0 ? 0 : split, cn = part == 0 ? split : n_rem - split;
-      if (row0 < t.m && cn > 0) epilogue_drain(taddr + c0, t, row0, col0 + c0, cn, (kWide ? 2 * UG_BN : UG_BN) - c0, epi_buf, lane);
+      float csum = 0.f;
+      if (row0 < t.m && cn > 0)
+        epilogue_drain(taddr + c0, t, row0, col0 + c0, cn, (kWide ? 2 * UG_BN : UG_BN) - c0, epi_buf, lane,
+                       P.checksum != 0 ? &csum : nullptr);
       if (tracer) trace_now(P, blockIdx.x, iter, UG_TR_EPI_END);
       tc_fence_before();
       mbar_arrive_cluster(mapa_shared(smem_u32(&sh->acc_empty[acc]), 0));
+      checksum_flush(P.checksum, csum, lane);
       if (C::kAccBufs == 2) acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }

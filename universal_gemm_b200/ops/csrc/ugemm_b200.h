@@ -91,6 +91,8 @@ typedef struct {
                              // zero at launch (the last worker to finish resets them): workers claim tiles dynamically
   int32_t fetch_depth;       // 16-byte loads a fetch-warp lane keeps in flight: 4, 8 or 16 (0 means 16)
   int32_t reserved0;
+  uint64_t checksum;         // 0 = off; else a double in device memory to which the kernel adds the sum of all accumulator
+                             // values it writes out (one atomic add per epilogue warp and tile); never reset by the kernel
 } UgFusedParams;
 
 // Fields of one timeline record (globaltimer nanoseconds unless noted).  Record `trace_slots` of a CTA is

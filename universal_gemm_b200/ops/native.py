@@ -84,6 +84,7 @@ class FusedParams(ctypes.Structure):
         ("trace", c_uint64), ("trace_slots", c_int32), ("epi_poll_ns", c_int32),
         ("sched", c_uint64),
         ("fetch_depth", c_int32), ("reserved0", c_int32),
+        ("checksum", c_uint64),
     ]
 
 
@@ -94,7 +95,7 @@ def check_layouts() -> None:
     assert SEGMENT_DTYPE.itemsize == 64, SEGMENT_DTYPE.itemsize
     assert TASK_DTYPE.itemsize == 64, TASK_DTYPE.itemsize
     assert PIECE_DTYPE.itemsize == 48, PIECE_DTYPE.itemsize
-    assert ctypes.sizeof(FusedParams) == 136, ctypes.sizeof(FusedParams)
+    assert ctypes.sizeof(FusedParams) == 144, ctypes.sizeof(FusedParams)
 
 
 check_layouts()

@@ -167,7 +167,8 @@ def _can_fuse(a: DistMatrix, b: DistMatrix, c: DistMatrix) -> bool:
 
 # ----------------------------------------------------------------------------- fused executor
 def _run_fused(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequence[MultiplyOp], *,
-               fuse_replica_reduce: bool = True, barriers: bool = True, beta: int = 1) -> None:
+               fuse_replica_reduce: bool = True, barriers: bool = True, beta: int = 1,
+               checksum: torch.Tensor | None = None) -> None:
     from ..ops.device import DeviceState
 
     world = c.world
@@ -189,7 +190,14 @@ def _run_fused(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: Sequ
             state.zero_2d(prog.clear_ptr, prog.num_clear * 4, 1, prog.num_clear * 4)
     if prof:
         e1.record()
-    prog.launch(state.stream())
+    if checksum is not None:
+        if checksum.dtype != torch.float64 or checksum.numel() < 1 or checksum.device != c.device:
+            raise ValueError("checksum must be a float64 tensor on the device of C")
+        prog.params.checksum = checksum.data_ptr()
+    try:
+        prog.launch(state.stream())
+    finally:
+        prog.params.checksum = 0
     state.launches += 1
     if prof:
         e2.record()
@@ -240,7 +248,8 @@ def _run_tilewise(kind: str, a: DistMatrix, b: DistMatrix, c: DistMatrix, ops: S
 
 # ----------------------------------------------------------------------------- entry points
 def _execute(kind: str, a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp] | None, *, local_only: bool,
-             executor: str | None, fuse_replica_reduce: bool, barriers: bool, beta: int = 1) -> list[MultiplyOp]:
+             executor: str | None, fuse_replica_reduce: bool, barriers: bool, beta: int = 1,
+             checksum: torch.Tensor | None = None) -> list[MultiplyOp]:
     if beta not in (0, 1):
         raise ValueError("beta must be 0 (C = A @ B) or 1 (C += A @ B)")
     a, b, c = resolve(a), resolve(b), resolve(c)
@@ -256,13 +265,16 @@ def _execute(kind: str, a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp] | None
             raise RuntimeError("the fused executor needs a CUDA world and bfloat16 (or float32) A / B")
         if rep_c > 1 and not fuse_replica_reduce and T.my_replica(c.layout, c.rank) != 0:
             c.local_padded.zero_()
-        _run_fused(kind, a, b, c, ops, fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta)
+        _run_fused(kind, a, b, c, ops, fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta,
+                   checksum=checksum)
         if rep_c > 1 and not fuse_replica_reduce:
             R.reduce_replicas(c)
             world.device_barrier()
         return list(ops)
     if executor != "tilewise":
         raise ValueError(f"unknown executor {executor!r}")
+    if checksum is not None:
+        raise ValueError("checksum= is computed by the fused kernel's epilogue; the tilewise executor has none")
     if beta == 0:
         c.local_padded.zero_()
     if rep_c > 1 and T.my_replica(c.layout, c.rank) != 0:
@@ -283,20 +295,24 @@ def _execute(kind: str, a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp] | None
 def execute_stationary_c(a: Any, b: Any, c: Any, *, local_only: bool = True, release_remote_tiles: bool = True,
                          use_async: bool | None = None, max_outstanding_prefetch: int = 1,
                          executor: str | None = None, fuse_replica_reduce: bool = True,
-                         barriers: bool = True, beta: int = 1) -> list[MultiplyOp]:
-    """``C += A @ B`` with the owner of every C tile computing it.  Returns the op list."""
+                         barriers: bool = True, beta: int = 1, checksum: torch.Tensor | None = None) -> list[MultiplyOp]:
+    """``C += A @ B`` with the owner of every C tile computing it.  Returns the op list.
+
+    ``checksum`` (fused executor): a float64 device tensor to whose first element this rank's kernel adds the sum of
+    all values it writes or adds into C in this call (its share of ``sum(A @ B)``); it is never reset."""
     return _execute("c", a, b, c, None, local_only=local_only, executor=executor,
-                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta)
+                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta, checksum=checksum)
 
 
 def execute_stationary_b(a: Any, b: Any, c: Any, *, local_only: bool = True, release_remote_tiles: bool = True,
                          use_async: bool | None = None, max_outstanding_prefetch: int = 1,
                          max_outstanding_accumulates: int = 4, num_compute_streams: int = 2,
                          executor: str | None = None, fuse_replica_reduce: bool = True,
-                         barriers: bool = True, beta: int = 1) -> list[MultiplyOp]:
-    """``C += A @ B`` with the owner of every B tile multiplying it and pushing partial C tiles."""
+                         barriers: bool = True, beta: int = 1, checksum: torch.Tensor | None = None) -> list[MultiplyOp]:
+    """``C += A @ B`` with the owner of every B tile multiplying it and pushing partial C tiles.
+    ``checksum``: see :func:`execute_stationary_c`."""
     return _execute("b", a, b, c, None, local_only=local_only, executor=executor,
-                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta)
+                    fuse_replica_reduce=fuse_replica_reduce, barriers=barriers, beta=beta, checksum=checksum)
 
 
 def execute_stationary_c_ops(a: Any, b: Any, c: Any, ops: Sequence[MultiplyOp], *, release_remote_tiles: bool = True,
