@@ -662,21 +662,27 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane, int dept
     else if (depth <= 8) copy_flat_vec<8>(pc, lane, vec_per_row, static_cast<uint32_t>(total));
     else copy_flat_vec<16>(pc, lane, vec_per_row, static_cast<uint32_t>(total));
   } else {
-    // Source only 2-byte aligned (odd column offsets or pitches of odd-shaped partitions): every 16-byte destination
-    // vector is gathered from eight 2-byte loads; four vectors per lane and batch keep 32 loads in flight.
+    // Source only 2-byte aligned (odd column offsets or pitches of odd-shaped partitions).  Every 16-byte destination
+    // vector is cut out of the two 16-byte-aligned source vectors that cover it (funnel shifts by the source's byte
+    // offset), so the copy still moves whole 16-byte vectors over the link: 2-byte loads from a peer cost a 32-byte
+    // sector each.  The second vector is only read when it holds needed bytes, so no read leaves the source row.
+    // Four destination vectors per lane and batch keep up to eight loads in flight.
     constexpr uint32_t U = 4;
     const uint32_t vpr = static_cast<uint32_t>(vec_per_row);
     const uint32_t nvec = static_cast<uint32_t>(total);
     for (uint32_t base = 0; base < nvec; base += 32u * U) {
-      uint16_t e[U][8];
+      uint4 lo[U], hi[U];
+      uint32_t shift[U];
 #pragma unroll
       for (uint32_t u = 0; u < U; ++u) {
         const uint32_t idx = min(base + u * 32u + static_cast<uint32_t>(lane), nvec - 1u);
         const uint32_t r = idx / vpr, c = idx - r * vpr;
-        const uint16_t* sp = reinterpret_cast<const uint16_t*>(src + static_cast<int64_t>(r) * pc.src_ld + (static_cast<int64_t>(c) << 4));
-        const int valid = min(8, (pc.row_bytes - static_cast<int>(c << 4)) >> 1);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) e[u][k] = (k < valid) ? ld_stream_u16(sp + k) : static_cast<uint16_t>(0);
+        const uint64_t sp = reinterpret_cast<uint64_t>(src) + static_cast<uint64_t>(r) * pc.src_ld + (static_cast<uint64_t>(c) << 4);
+        const int valid_bytes = min(16, pc.row_bytes - static_cast<int>(c << 4));
+        shift[u] = static_cast<uint32_t>(sp & 15u);
+        const char* ap = reinterpret_cast<const char*>(sp - shift[u]);
+        lo[u] = ld_stream_v4(ap);
+        hi[u] = (static_cast<int>(shift[u]) + valid_bytes > 16) ? ld_stream_v4(ap + 16) : make_uint4(0u, 0u, 0u, 0u);
       }
       asm volatile("" ::: "memory");
 #pragma unroll
@@ -684,12 +690,25 @@ __device__ __forceinline__ void copy_piece(const UgPiece& pc, int lane, int dept
         const uint32_t idx = base + u * 32u + static_cast<uint32_t>(lane);
         if (idx < nvec) {
           const uint32_t r = idx / vpr, c = idx - r * vpr;
-          uint4 out;
-          out.x = e[u][0] | (static_cast<uint32_t>(e[u][1]) << 16);
-          out.y = e[u][2] | (static_cast<uint32_t>(e[u][3]) << 16);
-          out.z = e[u][4] | (static_cast<uint32_t>(e[u][5]) << 16);
-          out.w = e[u][6] | (static_cast<uint32_t>(e[u][7]) << 16);
-          *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * pc.dst_ld + (static_cast<int64_t>(c) << 4)) = out;
+          const uint32_t w[9] = {lo[u].x, lo[u].y, lo[u].z, lo[u].w, hi[u].x, hi[u].y, hi[u].z, hi[u].w, 0u};
+          const uint32_t q = shift[u] >> 2, bits = (shift[u] & 3u) * 8u;
+          uint32_t o[4];
+#pragma unroll
+          for (uint32_t i = 0; i < 4; ++i) {
+            uint32_t a = 0u, b = 0u;
+#pragma unroll
+            for (uint32_t qq = 0; qq < 4; ++qq)
+              if (q == qq) { a = w[i + qq]; b = w[i + qq + 1]; }
+            o[i] = __funnelshift_r(a, b, bits);
+          }
+          const int valid = min(8, (pc.row_bytes - static_cast<int>(c << 4)) >> 1);     // elements inside the row
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (2 * i >= valid) o[i] = 0u;
+            else if (2 * i + 1 >= valid) o[i] &= 0xffffu;
+          }
+          *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * pc.dst_ld + (static_cast<int64_t>(c) << 4)) =
+              make_uint4(o[0], o[1], o[2], o[3]);
         }
       }
     }
